@@ -14,9 +14,14 @@ _ROOT = Path(__file__).resolve().parent
 HEADER_PATH = _ROOT.parent / "include" / "dnet_b200_seq.h"
 
 DN_SEQ_BF16, DN_SEQ_F32 = 0, 1
-DN_MIX_ATTENTION, DN_MIX_DELTA, DN_MIX_PARALLEL, DN_MIX_WKV = 0, 1, 2, 3
+DN_MIX_ATTENTION, DN_MIX_DELTA, DN_MIX_PARALLEL, DN_MIX_WKV, DN_MIX_LATENT = 0, 1, 2, 3, 4
+DN_MASK_BLOCK, DN_MASK_WINDOW = 0, 1
+DN_ROT_INTERLEAVED, DN_ROT_HALF = 0, 1
 DN_NORM_RMS, DN_NORM_DYT = 0, 1
 DN_MLP_DENSE, DN_MLP_MOE = 0, 1
+DN_FF_GEGLU, DN_FF_RELU2 = 0, 1
+DN_ROUTER_TOPK, DN_ROUTER_SCORED = 0, 1
+DN_EXPERT_CGLU, DN_EXPERT_SWIGLU = 0, 1
 # dn_seq_bind slots, in the header's order
 _LAYER_SLOTS = ["norm1", "norm2", "mix.q", "mix.k", "mix.v", "mix.o", "mix.q.conv", "mix.k.conv", "mix.v.conv", "mix.q.norm",
                 "mix.k.norm", "mix.a", "mix.b", "mix.g", "mix.A_log", "mix.dt_bias", "mix.norm", "mlp.gate", "mlp.up", "mlp.down",
@@ -27,7 +32,9 @@ _LAYER_SLOTS = ["norm1", "norm2", "mix.q", "mix.k", "mix.v", "mix.o", "mix.q.con
                 "r.q", "r.k", "r.v", "r.g", "r.o", "r.norm",
                 "decay1", "decay2", "decay.b",
                 "mu.r", "mu.k", "mu.v", "mu.g", "mu.w", "bonus",
-                "router", "router.b", "shared.gate", "shared.up", "shared.down"]
+                "router", "router.b", "shared.gate", "shared.up", "shared.down",
+                "mix.dq", "mix.dq.norm", "mix.dkv", "mix.dkv.norm", "mix.uk", "mix.uv",
+                "mlp.up.b", "mlp.down.b", "router.corr", "shared.sg"]
 LAYER_SLOT = {n: i for i, n in enumerate(_LAYER_SLOTS)}
 MODEL_SLOT = {"embed": 100, "final.norm": 101, "head": 102, "final.norm.b": 103, "final.norm.alpha": 104,
               "embed.norm": 105, "embed.norm.b": 106, "embed.norm.alpha": 107, "loop.in": 108}
@@ -45,7 +52,10 @@ class LayerCfg(C.Structure):
                 ("r_heads", C.c_int32), ("r_dim", C.c_int32), ("r_vdim", C.c_int32), ("rank", C.c_int32), ("tau", C.c_float),
                 ("left_scale", C.c_float), ("right_scale", C.c_float),
                 ("mlp_kind", C.c_int32), ("experts", C.c_int32), ("top", C.c_int32), ("limit", C.c_float),
-                ("shared_ff", C.c_int32), ("shared_limit", C.c_float)]
+                ("shared_ff", C.c_int32), ("shared_limit", C.c_float),
+                ("mask_kind", C.c_int32), ("rot_layout", C.c_int32), ("kv_rank", C.c_int32), ("q_rank", C.c_int32), ("rot_part", C.c_int32),
+                ("ff_act", C.c_int32), ("router_kind", C.c_int32), ("expert_act", C.c_int32), ("identity", C.c_int32),
+                ("groups", C.c_int32), ("groups_keep", C.c_int32), ("router_scale", C.c_float), ("shared_gate", C.c_int32)]
 
 
 class SeqCfg(C.Structure):
@@ -53,7 +63,7 @@ class SeqCfg(C.Structure):
                 ("eps", C.c_float), ("embed_scale", C.c_float), ("pool_pages", C.c_int32), ("max_seqs", C.c_int32),
                 ("max_batch_tokens", C.c_int32),
                 ("norm_kind", C.c_int32), ("post_norm", C.c_int32), ("embed_norm", C.c_int32), ("logit_softcap", C.c_float),
-                ("loop_start", C.c_int32), ("loop_stop", C.c_int32), ("loop_times", C.c_int32)]
+                ("loop_start", C.c_int32), ("loop_stop", C.c_int32), ("loop_times", C.c_int32), ("no_pre_norm", C.c_int32)]
 
 
 def declared_symbols() -> List[str]:

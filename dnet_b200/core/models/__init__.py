@@ -3,7 +3,7 @@ from typing import Any, List, Optional
 
 from .base import BaseRingModel, KVHandle
 from .llama import LlamaRingModel, MixtralRingModel, Qwen2RingModel
-from .seqmix import FilinexRingModel, MoputarRingModel, SeqHandle, SeqMixRingModel
+from .seqmix import FilinexRingModel, LutesunRingModel, MoputarRingModel, SeqHandle, SeqMixRingModel
 
 
 def _subclasses(cls):
@@ -29,5 +29,5 @@ def get_ring_model(model_type: str, model_config: Any, assigned_layers: Optional
     raise ValueError(f"Unsupported model type: {model_type}")
 
 
-__all__ = ["BaseRingModel", "FilinexRingModel", "KVHandle", "LlamaRingModel", "MixtralRingModel", "MoputarRingModel", "Qwen2RingModel", "SeqHandle",
+__all__ = ["BaseRingModel", "FilinexRingModel", "KVHandle", "LlamaRingModel", "LutesunRingModel", "MixtralRingModel", "MoputarRingModel", "Qwen2RingModel", "SeqHandle",
            "SeqMixRingModel", "get_ring_model", "ring_model_class"]

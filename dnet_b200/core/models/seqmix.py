@@ -33,6 +33,16 @@ rotation; no ``conv``: no convolution; no ``kv_from``: own keys and values).
 
 Sizes the config does not give (the inner size of the two-step decay projections, a wkv layer's value size) are
 read from the checkpoint's tensor shapes (``tensor_shapes``), or from the optional keys ``rank`` / ``vdim``.
+
+``LutesunRingModel`` is a list of latent-attention layers with dense or routed feed-forwards:
+
+    {"architecture": "Lutesun", "vocab": V, "width": W, "norm": {"eps": e}, "embedding": {"scale": c},
+     "layers": [{"type": "latent_attention" | "latent_attention_2",
+                 "mixer": {"heads", "dim", "rot_dim", "vdim", "kv_rank", "q_rank",   # q_rank: the second type only
+                           "scale", "rot": {"base", "dims"}, "mask": {"size"}},
+                 "mlp": {"kind": "dense", "ff": F}
+                      | {"kind": "moe", "router": {"experts", "top", "identity", "scale", "groups": {"count", "keep"}},
+                         "expert": {"ff"}, "shared": {"ff"} | null} | null}, ...]}
 """
 from __future__ import annotations
 
@@ -69,9 +79,10 @@ class SeqHandle:
         self.slot = -1
 
 
-def _attention_cfg(lc: _seqabi.LayerCfg, mx: dict, qk_norm: bool) -> None:
+def _attention_cfg(lc: _seqabi.LayerCfg, mx: dict, qk_norm: bool, mask: str = "block") -> None:
     lc.scale = float(mx.get("scale", float(mx["dim"]) ** -0.5))
     lc.chunk = int((mx.get("mask") or {}).get("size", 0))
+    lc.mask_kind = _seqabi.DN_MASK_WINDOW if mask == "window" else _seqabi.DN_MASK_BLOCK
     rot = mx.get("rot") or {}
     lc.rot_dims = int(rot.get("dims", 0))
     lc.rot_base = float(rot.get("base", 10000.0))
@@ -88,7 +99,8 @@ def parse_layer_list(cfg: dict, family: Optional[dict] = None,
     """config.json of a layer-list family -> the C structs.  Every size and constant comes from the config, or (what
     the config does not give) from a tensor's shape; ``family`` holds what a design fixes (kind of norm, norms after a
     sublayer and on the embedding, whether attention norms q and k, has a sink, gates its heads)."""
-    fam = {"norm": "rms", "post_norm": False, "embed_norm": False, "qk_norm": True, "sink": False, "head_gate": False}
+    fam = {"norm": "rms", "post_norm": False, "pre_norm": True, "embed_norm": False, "qk_norm": True, "sink": False, "head_gate": False,
+           "mask": "block", "ff_act": "geglu", "router": "topk", "expert_act": "cglu", "shared_gate": False}
     fam.update(family or {})
     shapes = shapes or {}
 
@@ -107,8 +119,18 @@ def parse_layer_list(cfg: dict, family: Optional[dict] = None,
         lc.kv_from = -1
         if kind == "attention":
             lc.mixer = _seqabi.DN_MIX_ATTENTION
-            _attention_cfg(lc, mx, fam["qk_norm"])
+            _attention_cfg(lc, mx, fam["qk_norm"], fam["mask"])
             lc.sink, lc.out_gate = int(fam["sink"]), int(fam["head_gate"])
+        elif kind in ("latent_attention", "latent_attention_2"):
+            # the second type sends its queries through a normed latent too, pairs rotary dims half apart and gates its heads
+            second = kind == "latent_attention_2"
+            lc.mixer = _seqabi.DN_MIX_LATENT
+            _attention_cfg(lc, {**mx, "kv_heads": 1}, False, fam["mask"])
+            lc.rot_part = int(mx.get("rot_dim", lc.rot_dims))
+            lc.kv_rank = int(mx["kv_rank"])
+            lc.q_rank = from_shape(f"l{i}.mix.dq", 0, mx, "q_rank", f"layer {i}") if second else 0
+            lc.rot_layout = _seqabi.DN_ROT_HALF if second else _seqabi.DN_ROT_INTERLEAVED
+            lc.out_gate = int(second)
         elif kind == "delta":
             lc.mixer = _seqabi.DN_MIX_DELTA
             lc.heads, lc.kv_heads = int(mx["heads"]), int(mx.get("kv_heads", mx["heads"]))
@@ -141,13 +163,26 @@ def parse_layer_list(cfg: dict, family: Optional[dict] = None,
             mk = mlp.get("kind", "dense")
             if mk == "dense":
                 lc.mlp_kind, lc.ff = _seqabi.DN_MLP_DENSE, int(mlp["ff"])
+                lc.ff_act = _seqabi.DN_FF_RELU2 if fam["ff_act"] == "relu2" else _seqabi.DN_FF_GEGLU
             elif mk == "moe":
                 lc.mlp_kind = _seqabi.DN_MLP_MOE
-                lc.ff, lc.limit = int(mlp["expert"]["ff"]), float(mlp["expert"]["limit"])
-                lc.experts, lc.top = int(mlp["router"]["experts"]), int(mlp["router"]["top"])
+                swiglu = fam["expert_act"] == "swiglu"
+                lc.expert_act = _seqabi.DN_EXPERT_SWIGLU if swiglu else _seqabi.DN_EXPERT_CGLU
+                lc.ff = int(mlp["expert"]["ff"])
+                lc.limit = float(mlp["expert"].get("limit", 0.0)) if swiglu else float(mlp["expert"]["limit"])
+                r = mlp["router"]
+                lc.experts, lc.top = int(r["experts"]), int(r["top"])
+                if fam["router"] == "scored":
+                    lc.router_kind = _seqabi.DN_ROUTER_SCORED
+                    lc.identity = int(r.get("identity", 0) or 0)
+                    g = r.get("groups") or {}
+                    lc.groups, lc.groups_keep = int(g.get("count", 0) or 0), int(g.get("keep", g.get("count", 0)) or 0)
+                    lc.router_scale = float(r.get("scale", 1.0))
                 sh = mlp.get("shared")
                 if sh:
-                    lc.shared_ff, lc.shared_limit = int(sh["ff"]), float(sh["limit"])
+                    lc.shared_ff = int(sh["ff"])
+                    lc.shared_limit = float(sh.get("limit", 0.0)) if swiglu else float(sh["limit"])
+                    lc.shared_gate = int(fam["shared_gate"])
             else:
                 raise ValueError(f"layer {i}: feed-forward kind {mk!r} unsupported")
         layers.append(lc)
@@ -155,7 +190,7 @@ def parse_layer_list(cfg: dict, family: Optional[dict] = None,
                         eps=float((cfg.get("norm") or {}).get("eps", 1e-6)),
                         embed_scale=float((cfg.get("embedding") or {}).get("scale", 1.0)))
     sc.norm_kind = _seqabi.DN_NORM_DYT if fam["norm"] == "dyt" else _seqabi.DN_NORM_RMS
-    sc.post_norm, sc.embed_norm = int(fam["post_norm"]), int(fam["embed_norm"])
+    sc.post_norm, sc.embed_norm, sc.no_pre_norm = int(fam["post_norm"]), int(fam["embed_norm"]), int(not fam["pre_norm"])
     sc.logit_softcap = float(cfg.get("logit_softcap", 0.0) or 0.0)
     lp = cfg.get("loop")
     if lp:
@@ -216,7 +251,9 @@ class SeqMixRingModel(BaseRingModel):
         W, V, S = self.hidden_size, self.vocab_size, int(self._cfg_struct.streams)
         sc = self._cfg_struct
         dyt = sc.norm_kind == _seqabi.DN_NORM_DYT
-        out: Dict[str, Tuple[int, ...]] = {"embed": (V, W), "final.norm": (W,), "head": (V, W)}
+        out: Dict[str, Tuple[int, ...]] = {"embed": (V, W), "final.norm": (W,)}
+        if not self.family.get("tied_head"):
+            out["head"] = (V, W)
 
         def norm(name: str) -> None:
             out[name] = (W,)
@@ -231,17 +268,28 @@ class SeqMixRingModel(BaseRingModel):
         for i, lc in enumerate(self._layer_structs):
             p = f"l{i}."
             att = lc.mixer in (_seqabi.DN_MIX_ATTENTION, _seqabi.DN_MIX_PARALLEL)
+            latent = lc.mixer == _seqabi.DN_MIX_LATENT
             cq = (lc.heads if lc.mixer != _seqabi.DN_MIX_DELTA else lc.kv_heads) * lc.dim
             ck, cv = lc.kv_heads * lc.dim, (lc.kv_heads if att else lc.heads) * lc.vdim
             co = lc.heads * lc.vdim
-            own = not (att and lc.kv_from >= 0)
-            norm(p + "norm1")
+            own = not (att and lc.kv_from >= 0) and not latent
+            if not sc.no_pre_norm:
+                norm(p + "norm1")
             if sc.post_norm:
                 norm(p + "post1")
             out[p + "mix.q"] = (cq, W)
             out[p + "mix.o"] = (W, co)
             if own:
                 out[p + "mix.k"], out[p + "mix.v"] = (ck, W), (cv, W)
+            if latent:
+                cq = lc.heads * (lc.dim + lc.rot_part)
+                out[p + "mix.q"] = (cq, lc.q_rank if lc.q_rank > 0 else W)
+                if lc.q_rank > 0:
+                    out[p + "mix.dq"], out[p + "mix.dq.norm"] = (lc.q_rank, W), (lc.q_rank,)
+                out[p + "mix.dkv"], out[p + "mix.dkv.norm"] = (lc.kv_rank + lc.rot_part, W), (lc.kv_rank,)
+                out[p + "mix.uk"], out[p + "mix.uv"] = (lc.heads * lc.dim, lc.kv_rank), (co, lc.kv_rank)
+                if lc.out_gate:
+                    out[p + "head_gate"] = (lc.heads, W)
             if lc.conv > 0:
                 out[p + "mix.q.conv"] = (cq, lc.conv)
                 if own:
@@ -273,17 +321,26 @@ class SeqMixRingModel(BaseRingModel):
                 out[p + "mix.A_log"] = out[p + "mix.dt_bias"] = (lc.heads,)
                 out[p + "mix.norm"] = (lc.vdim,)
             if lc.ff > 0:
-                norm(p + "norm2")
+                if not sc.no_pre_norm:
+                    norm(p + "norm2")
                 if sc.post_norm:
                     norm(p + "post2")
                 if lc.mlp_kind == _seqabi.DN_MLP_MOE:
-                    out[p + "router"], out[p + "router.b"] = (lc.experts, W), (lc.experts,)
+                    if lc.router_kind == _seqabi.DN_ROUTER_SCORED:
+                        out[p + "router"], out[p + "router.corr"] = (lc.experts + lc.identity, W), (lc.experts + lc.identity,)
+                    else:
+                        out[p + "router"], out[p + "router.b"] = (lc.experts, W), (lc.experts,)
+                    if lc.shared_ff > 0 and lc.shared_gate:
+                        out[p + "shared.sg"] = (1, W)
                     for e in range(lc.experts):
                         out[f"{p}mlp.e{e}.gate"] = out[f"{p}mlp.e{e}.up"] = (lc.ff, W)
                         out[f"{p}mlp.e{e}.down"] = (W, lc.ff)
                     if lc.shared_ff > 0:
                         out[p + "shared.gate"] = out[p + "shared.up"] = (lc.shared_ff, W)
                         out[p + "shared.down"] = (W, lc.shared_ff)
+                elif lc.ff_act == _seqabi.DN_FF_RELU2:
+                    out[p + "mlp.up"], out[p + "mlp.up.b"] = (lc.ff, W), (lc.ff,)
+                    out[p + "mlp.down"], out[p + "mlp.down.b"] = (W, lc.ff), (W,)
                 else:
                     out[p + "mlp.gate"] = out[p + "mlp.up"] = (lc.ff, W)
                     out[p + "mlp.down"] = (W, lc.ff)
@@ -333,6 +390,8 @@ class SeqMixRingModel(BaseRingModel):
                 else:
                     _seqabi.check(self._lib.dn_seq_bind(self._h, int(lname[1:]), _seqabi.LAYER_SLOT[suffix], t.data_ptr()))
             self._bound[key] = t     # keep the borrowed memory alive
+        if self.family.get("tied_head") and "embed" in self._bound:      # logits = embedding table x, the table itself
+            _seqabi.check(self._lib.dn_seq_bind(self._h, -1, _seqabi.MODEL_SLOT["head"], self._bound["embed"].data_ptr()))
         return self
 
     def missing_tensors(self) -> List[str]:
@@ -457,4 +516,20 @@ class FilinexRingModel(SeqMixRingModel):
                      "mix.right.a2.b": "decay.b"},
         "wkv": {"mix.r": "mix.q", "mix.mu.r": "mu.r", "mix.mu.k": "mu.k", "mix.mu.v": "mu.v", "mix.mu.g": "mu.g", "mix.mu.w": "mu.w",
                 "mix.w1": "decay1", "mix.w2": "decay2", "mix.w0": "decay.b", "mix.u": "bonus"},
+    }
+
+
+class LutesunRingModel(SeqMixRingModel):
+    """Lutesun: latent-attention layers under a sliding window -- the cache keeps one compressed row per token, of which
+    every head's keys and values are up-projections; the second layer type also compresses its queries, pairs rotary dims
+    half apart and gates its heads --, RMS norms on the sublayers' outputs only, a dense relu-squared feed-forward with
+    biases or experts routed by corrected, group-limited softmax scores (identity experts among them) with a gated shared
+    expert; scaled embedding whose table is also the output head."""
+
+    model_type = "lutesun"
+    family = {"norm": "rms", "post_norm": True, "pre_norm": False, "qk_norm": False, "tied_head": True, "mask": "window",
+              "ff_act": "relu2", "router": "scored", "expert_act": "swiglu", "shared_gate": True}
+    tensor_alias = {
+        "*": {"norm1": "post1", "norm2": "post2", **_MOE_ALIAS, "mlp.correction": "router.corr", "mlp.shared.sg": "shared.sg"},
+        "latent_attention_2": {"mix.uq": "mix.q", "mix.g": "head_gate"},
     }

@@ -4,6 +4,7 @@
 #include "dn_seq_kernels.cuh"
 #include "dn_seq_recur.cuh"
 #include "dn_seq_moe.cuh"
+#include "dn_seq_latent.cuh"
 #include "dn_gemm_tc.cuh"      // the tcgen05 / TMA GEMM the llama-family prefill runs on (namespace dn)
 #include "../../include/dnet_b200_seq.h"
 
@@ -61,6 +62,7 @@ struct SeqLayer {
   XMaps x_mo_r, x_lr;           // the linear-attention half's [MB, Rv]; the decay projection's inner [MB, rank]
   int Cq, Ck, Cv, Co;           // projection widths: q, k, v and the mixer's output before W_o
   int Rc, Rv;                   // linear-attention half of a parallel mixer: q / k width, v / output width
+  int Cql, Col;                 // latent attention: widths of the absorbed queries [H (R + rot)] and of the output in latent space [H R]
   float* inv_freq;              // [rot/2] device
   std::vector<const void*> etab_h;   // routed experts: [3][E] gate, up, down
   const void** etab_d;
@@ -93,7 +95,8 @@ struct dn_seq_model {
   int S1 = 1, MB = 0, max_pages = 0;
   // scratch
   float *xs = nullptr, *y = nullptr, *pa = nullptr, *pb = nullptr, *qn = nullptr, *kn = nullptr, *vv = nullptr, *od = nullptr,
-        *beta = nullptr, *decay = nullptr, *y2 = nullptr, *x0 = nullptr, *dz = nullptr, *rwt = nullptr, *eo = nullptr;
+        *beta = nullptr, *decay = nullptr, *y2 = nullptr, *x0 = nullptr, *dz = nullptr, *rwt = nullptr, *eo = nullptr, *sgate = nullptr;
+  int part_dv = 256;            // widest value row (padded to 32) of a split attention row's partials
   void *h = nullptr, *uq = nullptr, *uk = nullptr, *uv = nullptr, *qb = nullptr, *mo = nullptr, *gt = nullptr, *act = nullptr, *cat = nullptr,
        *xm = nullptr, *lr = nullptr, *eact = nullptr;
   int32_t *ridx = nullptr, *rpos = nullptr, *rtok = nullptr, *tiles = nullptr;
@@ -194,7 +197,7 @@ extern "C" int dn_seq_model_destroy(dn_seq_model* m) {
   cudaDeviceSynchronize();
   void* ptrs[] = {m->xs, m->y, m->pa, m->pb, m->qn, m->kn, m->vv, m->od, m->beta, m->decay, m->h, m->uq, m->uk, m->uv, m->qb,
                   m->mo, m->gt, m->act, m->conv_state, m->delta_state, m->stage_d, m->bt_d, m->tc_err, m->y2, m->x0, m->dz, m->rwt,
-                  m->eo, m->cat, m->xm, m->lr, m->eact, m->ridx, m->rpos, m->rtok, m->tiles, m->xg, m->attn_part};
+                  m->eo, m->cat, m->xm, m->lr, m->eact, m->ridx, m->rpos, m->rtok, m->tiles, m->xg, m->attn_part, m->sgate};
   for (void* p : ptrs) if (p) cudaFree(p);
   for (auto& g : m->graphs) cudaGraphExecDestroy(g.second.first);
   if (m->lg_buf) cudaFree(m->lg_buf);
@@ -232,8 +235,9 @@ extern "C" int dn_seq_model_create(const dn_seq_cfg* cfg, const dn_seq_layer_cfg
   if (looped && (cfg->loop_start < 0 || cfg->loop_stop > cfg->n_layers || cfg->loop_start >= cfg->loop_stop))
     rc = fail(DN_EINVAL, "loop [%d, %d) x %d does not fit %d layers", cfg->loop_start, cfg->loop_stop, cfg->loop_times, cfg->n_layers);
   if (rc == DN_OK && cfg->norm_kind != DN_NORM_RMS && cfg->norm_kind != DN_NORM_DYT) rc = fail(DN_EINVAL, "norm kind %d unknown", cfg->norm_kind);
-  if (rc == DN_OK && cfg->norm_kind == DN_NORM_RMS && (cfg->post_norm || cfg->embed_norm))
-    rc = fail(DN_EINVAL, "norms after a sublayer and on the embedding exist as dynamic tanh only");
+  if (rc == DN_OK && cfg->norm_kind == DN_NORM_RMS && cfg->embed_norm) rc = fail(DN_EINVAL, "a norm on the embedding exists as dynamic tanh only");
+  if (rc == DN_OK && cfg->norm_kind == DN_NORM_RMS && cfg->post_norm && cfg->streams > 0)
+    rc = fail(DN_EINVAL, "an RMS norm after a sublayer joins the plain residual only (streams = 0)");
   for (int i = 0; i < cfg->n_layers && rc == DN_OK; i++) {
     SeqLayer& l = m->L[i];
     l.c = layers[i];
@@ -243,7 +247,7 @@ extern "C" int dn_seq_model_create(const dn_seq_cfg* cfg, const dn_seq_layer_cfg
     l.etab_d = nullptr;
     l.emaps_d = nullptr;
     l.x_eact_ok = false;
-    l.Rc = l.Rv = 0;
+    l.Rc = l.Rv = l.Cql = l.Col = 0;
     const dn_seq_layer_cfg& c = l.c;
     if (c.heads <= 0 || c.kv_heads <= 0 || c.heads % c.kv_heads || c.dim <= 0 || c.vdim <= 0) {
       rc = fail(DN_EINVAL, "layer %d: heads %d / kv_heads %d / dim %d / vdim %d unsupported", i, c.heads, c.kv_heads, c.dim, c.vdim);
@@ -284,6 +288,27 @@ extern "C" int dn_seq_model_create(const dn_seq_cfg* cfg, const dn_seq_layer_cfg
         mrank = std::max(mrank, c.rank);
         mh = std::max(mh, c.r_heads);
       }
+    } else if (c.mixer == DN_MIX_LATENT) {
+      if (c.kv_rank <= 0 || c.kv_rank > 512 || c.q_rank < 0 || c.rot_part < 0 || c.rot_dims < 0 || c.rot_dims > c.rot_part || (c.rot_dims & 1) ||
+          c.kv_heads != 1 || c.conv > 0 || c.kv_from >= 0 || c.sink || c.qk_norm) {
+        rc = fail(DN_EINVAL, "layer %d: latent attention with kv_rank %d (1..512) / q_rank %d / rotated part %d of which %d turn unsupported", i,
+                  c.kv_rank, c.q_rank, c.rot_part, c.rot_dims);
+        break;
+      }
+      l.Cq = c.heads * (c.dim + c.rot_part);
+      l.Ck = c.kv_rank + c.rot_part;       // the cached row: [latent; rotated key part]
+      l.Cv = 0;
+      l.Co = c.heads * c.vdim;
+      l.Cql = c.heads * l.Ck;
+      l.Col = c.heads * c.kv_rank;
+      mrank = std::max(mrank, c.q_rank);
+      m->part_dv = std::max(m->part_dv, (c.kv_rank + 31) / 32 * 32);
+      if (c.rot_dims > 0) {
+        std::vector<float> f(c.rot_dims / 2);
+        for (int j = 0; j < c.rot_dims / 2; j++) f[j] = (float)std::pow((double)c.rot_base, -2.0 * j / (double)c.rot_dims);
+        if ((rc = dalloc(&l.inv_freq, f.size() * 4)) != DN_OK) break;
+        if (cudaMemcpy(l.inv_freq, f.data(), f.size() * 4, cudaMemcpyHostToDevice) != cudaSuccess) { rc = fail(DN_ECUDA, "inv_freq upload failed"); break; }
+      }
     } else if (c.mixer == DN_MIX_DELTA) {
       if (c.dim > 1024) { rc = fail(DN_EINVAL, "layer %d: delta dim %d > 1024", i, c.dim); break; }
       l.Cq = l.Ck = c.kv_heads * c.dim;
@@ -301,8 +326,20 @@ extern "C" int dn_seq_model_create(const dn_seq_cfg* cfg, const dn_seq_layer_cfg
       break;
     }
     if (c.mlp_kind == DN_MLP_MOE && c.ff > 0) {
-      if (c.experts <= 0 || c.experts > 4096 || c.top <= 0 || c.top > 16 || c.top > c.experts || c.shared_ff < 0) {
+      const int Et = c.experts + (c.router_kind == DN_ROUTER_SCORED ? c.identity : 0);
+      if (c.experts <= 0 || c.experts > 4096 || c.top <= 0 || c.top > 16 || c.top > Et || c.shared_ff < 0) {
         rc = fail(DN_EINVAL, "layer %d: %d experts / top %d unsupported (top <= 16, <= experts)", i, c.experts, c.top);
+        break;
+      }
+      if (c.router_kind != DN_ROUTER_TOPK && c.router_kind != DN_ROUTER_SCORED) { rc = fail(DN_EINVAL, "layer %d: router kind %d unknown", i, c.router_kind); break; }
+      if (c.expert_act != DN_EXPERT_CGLU && c.expert_act != DN_EXPERT_SWIGLU) { rc = fail(DN_EINVAL, "layer %d: expert activation %d unknown", i, c.expert_act); break; }
+      if (c.router_kind == DN_ROUTER_SCORED && (c.identity < 0 || c.groups < 0 || c.groups > 256 ||
+                                                (c.groups > 0 && (Et % c.groups || c.groups_keep < 1 || c.groups_keep > c.groups)))) {
+        rc = fail(DN_EINVAL, "layer %d: %d + %d experts in %d groups of which %d are kept unsupported", i, c.experts, c.identity, c.groups, c.groups_keep);
+        break;
+      }
+      if ((c.shared_gate || (c.router_kind == DN_ROUTER_SCORED && c.identity > 0)) && !(cfg->post_norm && cfg->streams <= 0)) {
+        rc = fail(DN_EINVAL, "layer %d: a gated shared expert and identity experts are joined by the kernels of a norm after the sublayer on the plain residual", i);
         break;
       }
       l.etab_h.assign((size_t)3 * c.experts, nullptr);
@@ -311,14 +348,16 @@ extern "C" int dn_seq_model_create(const dn_seq_cfg* cfg, const dn_seq_layer_cfg
       if (cfg->dtype == DN_SEQ_BF16 && (rc = dalloc(&l.emaps_d, (size_t)3 * c.experts * sizeof(CUtensorMap))) != DN_OK) break;
       mpairs = std::max(mpairs, c.top);
       meff = std::max(meff, c.ff);
-      mexp = std::max(mexp, c.experts);
+      mexp = std::max(mexp, Et);
       mff = std::max(mff, c.shared_ff);
     } else if (c.mlp_kind != DN_MLP_DENSE && c.ff > 0) {
       rc = fail(DN_EINVAL, "layer %d: feed-forward kind %d unknown", i, c.mlp_kind);
       break;
     } else {
+      if (c.ff > 0 && c.ff_act != DN_FF_GEGLU && c.ff_act != DN_FF_RELU2) { rc = fail(DN_EINVAL, "layer %d: feed-forward activation %d unknown", i, c.ff_act); break; }
       mff = std::max(mff, c.ff);
     }
+    mq = std::max(mq, l.Cql); mo = std::max(mo, l.Col);
     mq = std::max(mq, std::max(l.Cq, l.Rc)); mk = std::max(mk, std::max(l.Ck, l.Rc)); mv = std::max(mv, std::max(l.Cv, l.Rv));
     mo = std::max(mo, std::max(l.Co, l.Rv));
     mh = std::max(mh, c.heads);
@@ -339,7 +378,7 @@ extern "C" int dn_seq_model_create(const dn_seq_cfg* cfg, const dn_seq_layer_cfg
       Run r{o.first, o.second, -1, 0, 0};
       const SeqLayer& l = m->L[r.layer];
       const dn_seq_layer_cfg& c = l.c;
-      if (c.mixer == DN_MIX_ATTENTION || c.mixer == DN_MIX_PARALLEL) {
+      if (c.mixer == DN_MIX_ATTENTION || c.mixer == DN_MIX_PARALLEL || c.mixer == DN_MIX_LATENT) {
         if (c.kv_from >= 0) r.kv_index = m->runs[last_run[c.kv_from]].kv_index;
         else {
           r.kv_index = (int)m->kpool.size();
@@ -367,7 +406,8 @@ extern "C" int dn_seq_model_create(const dn_seq_cfg* cfg, const dn_seq_layer_cfg
   DA(m->qn, MB * mdq * 4); DA(m->kn, MB * mdq * 4); DA(m->vv, MB * mo * 4); DA(m->od, MB * mo * 4);
   DA(m->beta, MB * mh * 4); DA(m->decay, MB * mh * 4);
   DA(m->y2, MB * W * 4); DA(m->dz, MB * mdq * 4); DA(m->lr, MB * mrank * e);
-  DA(m->attn_part, (size_t)AT_SPLIT_ROWS * mh * AT_MAX_SPLITS * (2 + 256) * 4);
+  DA(m->attn_part, (size_t)AT_SPLIT_ROWS * mh * AT_MAX_SPLITS * (2 + m->part_dv) * 4);
+  DA(m->sgate, MB * 4);
   if (looped) { DA(m->x0, MB * W * 4); DA(m->cat, MB * 2 * W * e); }
   if (any_wkv) DA(m->xm, (size_t)SHIFT_MAX * MB * W * e);
   if (mpairs > 0) {
@@ -391,6 +431,7 @@ extern "C" int dn_seq_model_create(const dn_seq_cfg* cfg, const dn_seq_layer_cfg
       make_xmaps(&l.x_mo, m->mo, m->MB, l.Co);
       if (l.Rv > 0) make_xmaps(&l.x_mo_r, m->mo, m->MB, l.Rv);
       if (l.c.rank > 0) make_xmaps(&l.x_lr, m->lr, m->MB, l.c.rank);
+      if (l.c.mixer == DN_MIX_LATENT && l.c.q_rank > 0) make_xmaps(&l.x_lr, m->lr, m->MB, l.c.q_rank);
       const int fa = l.c.mlp_kind == DN_MLP_MOE ? l.c.shared_ff : l.c.ff;
       if (fa > 0) make_xmaps(&l.x_act, m->act, m->MB, fa);
     }
@@ -437,7 +478,9 @@ extern "C" int dn_seq_bind(dn_seq_model* m, int layer, int which, const void* p)
   l.w[which] = p;
   int rows = 0, cols = m->cfg.width;
   switch (which) {
-    case DN_SQ_Q: rows = l.Cq; break;
+    case DN_SQ_Q: rows = l.Cq; if (l.c.mixer == DN_MIX_LATENT && l.c.q_rank > 0) cols = l.c.q_rank; break;
+    case DN_SQ_DQ: rows = l.c.q_rank; break;
+    case DN_SQ_DKV: rows = l.Ck; break;
     case DN_SQ_K: rows = l.Ck; break;
     case DN_SQ_V: rows = l.Cv; break;
     case DN_SQ_G: rows = l.Co; break;
@@ -575,9 +618,10 @@ static cudaError_t gemm_tc(const CUtensorMap& w, const CUtensorMap& w2, const XM
 struct LinMaps { const CUtensorMap* w; const CUtensorMap* w2; const XMaps* x; };
 template <class T>
 static cudaError_t linear(dn_seq_model* m, cudaStream_t s, const T* X, const void* W, const void* W2, void* Y, int N, int O, int K, bool out32,
-                          int act, LinMaps tm = LinMaps{nullptr, nullptr, nullptr}, float alim = 0.f) {
+                          int act, LinMaps tm = LinMaps{nullptr, nullptr, nullptr}, float alim = 0.f, const void* bias = nullptr) {
   // (a weight of fewer than 128 rows fills part of a tile: still far ahead of the CUDA-core tiles once K is in the thousands)
-  if (std::is_same<T, bf16>::value && N >= 16 && O >= 16 && tm.w && tm.x && tm.x->ok && (act == ACT_NONE || act == ACT_TANH || ((act == ACT_GEGLU || act == ACT_CGLU) && tm.w2))) {
+  if (std::is_same<T, bf16>::value && N >= 16 && O >= 16 && tm.w && tm.x && tm.x->ok && !bias &&
+      (act == ACT_NONE || act == ACT_TANH || ((act == ACT_GEGLU || act == ACT_CGLU) && tm.w2))) {
     dn::TcParams p;
     memset(&p, 0, sizeof(p));
     p.T = N; p.N = O; p.K = K; p.ldy = O; p.Y = (dn::bf16*)Y; p.err = m->tc_err; p.limit = alim;
@@ -589,12 +633,12 @@ static cudaError_t linear(dn_seq_model* m, cudaStream_t s, const T* X, const voi
   }
   if (N <= 8) {
     dim3 grid((O + 7) / 8);
-    if (out32) return launch(k_linear_rows<T, true>, grid, dim3(256), 0, s, X, (const T*)W, (const T*)W2, Y, N, O, K, act, alim);
-    return launch(k_linear_rows<T, false>, grid, dim3(256), 0, s, X, (const T*)W, (const T*)W2, Y, N, O, K, act, alim);
+    if (out32) return launch(k_linear_rows<T, true>, grid, dim3(256), 0, s, X, (const T*)W, (const T*)W2, Y, N, O, K, act, alim, (const T*)bias);
+    return launch(k_linear_rows<T, false>, grid, dim3(256), 0, s, X, (const T*)W, (const T*)W2, Y, N, O, K, act, alim, (const T*)bias);
   }
   dim3 grid((O + 63) / 64, (N + 63) / 64);
-  if (out32) return launch(k_linear<T, true>, grid, dim3(256), 0, s, X, (const T*)W, (const T*)W2, Y, N, O, K, act, alim);
-  return launch(k_linear<T, false>, grid, dim3(256), 0, s, X, (const T*)W, (const T*)W2, Y, N, O, K, act, alim);
+  if (out32) return launch(k_linear<T, true>, grid, dim3(256), 0, s, X, (const T*)W, (const T*)W2, Y, N, O, K, act, alim, (const T*)bias);
+  return launch(k_linear<T, false>, grid, dim3(256), 0, s, X, (const T*)W, (const T*)W2, Y, N, O, K, act, alim, (const T*)bias);
 }
 
 // Attention of a step: bf16 steps that bring a prompt portion (an entry of 16 tokens or more) run on the MMA tiles when
@@ -656,33 +700,40 @@ static cudaError_t gemm_tc_grouped(const CUtensorMap& x, const dn::TcParams& p, 
 
 // the expert products of a routed feed-forward: h [N, W] -> m->y [N, W] (routed sum), m->y2 (shared expert, if any);
 // fused: the sum of both goes through the norm after the sublayer into the plain residual in the combining kernel
+// combine = false: the caller's joining kernel adds the pairs itself (k_rms_join)
 template <class T>
-static int moe_ff(dn_seq_model* m, SeqLayer& l, int N, bool fused, NextNorm<T> nx, cudaStream_t s) {
+static int moe_ff(dn_seq_model* m, SeqLayer& l, int N, bool fused, NextNorm<T> nx, cudaStream_t s, bool combine = true) {
   const dn_seq_layer_cfg& lc = l.c;
-  const int W = m->cfg.width, E = lc.experts, top = lc.top, P = N * top;
+  const bool scored = lc.router_kind == DN_ROUTER_SCORED;
+  const int W = m->cfg.width, E = lc.experts, Et = E + (scored ? lc.identity : 0), top = lc.top, P = N * top;
+  const int eact = lc.expert_act == DN_EXPERT_SWIGLU ? ACT_SWIGLU : ACT_CGLU;
   auto w = [&](int i) { return (const T*)l.w[i]; };
   auto wm = [&](int i) { return l.tm_ok[i] ? &l.tm[i] : (const CUtensorMap*)nullptr; };
   CK(mark(m, DN_SEQ_PH_ROUTER, s));
-  CK(launch(k_router<T>, dim3(N), dim3(32 * std::min(32, std::max(4, E))), (size_t)E * 4, s, (const T*)m->h, w(DN_SQ_ROUTER), w(DN_SQ_ROUTER_B), W, E, top, m->ridx, m->rwt, m->rpos));
+  if (scored)
+    CK(launch(k_router_scored<T>, dim3(N), dim3(32 * std::min(32, std::max(4, Et + 1))), (size_t)2 * Et * 4, s, (const T*)m->h, w(DN_SQ_ROUTER), w(DN_SQ_ROUTER_CORR),
+              W, Et, top, lc.groups, lc.groups_keep, lc.router_scale, lc.shared_gate ? w(DN_SQ_SH_SG) : (const T*)nullptr, m->ridx, m->rwt, m->rpos, m->sgate));
+  else
+    CK(launch(k_router<T>, dim3(N), dim3(32 * std::min(32, std::max(4, E))), (size_t)E * 4, s, (const T*)m->h, w(DN_SQ_ROUTER), w(DN_SQ_ROUTER_B), W, E, top, m->ridx, m->rwt, m->rpos));
   const bool few = N <= 8;
   if (few) {      // the shared expert's rows ride in the same two launches
     SharedExpert sh{l.w[DN_SQ_SH_GATE], l.w[DN_SQ_SH_UP], l.w[DN_SQ_SH_DOWN], lc.shared_ff, lc.shared_limit, m->act, m->y2};
     const int rows = P + (lc.shared_ff > 0 ? N : 0);
     CK(mark(m, DN_SEQ_PH_MOE_UP, s));
     CK(launch(k_moe_rows<T, true>, dim3((std::max(lc.ff, lc.shared_ff) + 7) / 8, rows), dim3(256), 0, s, (const T*)m->h, (const void* const*)l.etab_d, E,
-              (const int32_t*)m->ridx, top, m->eact, lc.ff, W, lc.limit, P, (const T*)m->h, sh));
+              (const int32_t*)m->ridx, top, m->eact, lc.ff, W, lc.limit, P, (const T*)m->h, sh, eact));
     CK(mark(m, DN_SEQ_PH_MOE_DOWN, s));
     CK(launch(k_moe_rows<T, false>, dim3((W + 7) / 8, rows), dim3(256), 0, s, (const T*)m->eact, (const void* const*)l.etab_d, E, (const int32_t*)m->ridx, top,
-              m->eo, W, lc.ff, 0.f, P, (const T*)m->h, sh));
+              m->eo, W, lc.ff, 0.f, P, (const T*)m->h, sh, eact));
   } else {
     MoePlan pl{m->rpos, m->rtok, m->tiles, m->tiles + m->max_tiles, m->tiles + 2 * m->max_tiles, m->tiles + 3 * m->max_tiles};
     const int mt = std::min(m->max_tiles, P / MOE_ROWS + E + 1);
-    bool tc = std::is_same<T, bf16>::value && m->x_xg_ok && l.x_eact_ok && l.emaps_d && lc.ff >= 32 && W >= 32;
+    bool tc = std::is_same<T, bf16>::value && m->x_xg_ok && l.x_eact_ok && l.emaps_d && lc.ff >= 32 && W >= 32 && eact == ACT_CGLU;
     for (char ok : l.emap_ok) tc = tc && ok;
     // rows of a token tile: 128 (the tensor cores read the weight tile once for twice the tokens) when an expert gets
     // two such tiles on average, else 64 (less padding); the CUDA-core tiles are 64 rows
     const int tile_rows = tc && P / E >= 256 ? 128 : MOE_ROWS;
-    CK(launch(k_moe_plan, dim3(1), dim3(1024), (size_t)(2 * E + 1) * 4, s, (const int32_t*)m->ridx, P, top, E, tile_rows, pl));
+    CK(launch(k_moe_plan, dim3(1), dim3(1024), (size_t)(2 * Et + 1) * 4, s, (const int32_t*)m->ridx, P, top, Et, tile_rows, pl, E));
     if (tc) {     // bf16 with TMA-able shapes: every expert's tiles in one launch of the tcgen05 GEMM
       CK(launch(k_moe_gather<T>, dim3(P), dim3(128), 0, s, (const T*)m->h, (const int32_t*)m->rtok, W, (T*)m->xg));
       dn::TcParams p;
@@ -699,21 +750,23 @@ static int moe_ff(dn_seq_model* m, SeqLayer& l, int N, bool fused, NextNorm<T> n
       else CK(gemm_tc_grouped<dn::EPI_STORE_F32, 64>(l.x_eact[0], p, s));
     } else {
       CK(mark(m, DN_SEQ_PH_MOE_UP, s));
-      CK(launch(k_moe_tiles<T, true>, dim3((lc.ff + 63) / 64, mt), dim3(256), 0, s, (const T*)m->h, (const void* const*)l.etab_d, E, pl, m->eact, lc.ff, W, lc.limit));
+      CK(launch(k_moe_tiles<T, true>, dim3((lc.ff + 63) / 64, mt), dim3(256), 0, s, (const T*)m->h, (const void* const*)l.etab_d, E, pl, m->eact, lc.ff, W, lc.limit, eact));
       CK(mark(m, DN_SEQ_PH_MOE_DOWN, s));
-      CK(launch(k_moe_tiles<T, false>, dim3((W + 63) / 64, mt), dim3(256), 0, s, (const T*)m->eact, (const void* const*)l.etab_d, E, pl, m->eo, W, lc.ff, 0.f));
+      CK(launch(k_moe_tiles<T, false>, dim3((W + 63) / 64, mt), dim3(256), 0, s, (const T*)m->eact, (const void* const*)l.etab_d, E, pl, m->eo, W, lc.ff, 0.f, eact));
     }
   }
   if (lc.shared_ff > 0 && !few) {
     CK(mark(m, DN_SEQ_PH_FF_UP, s));
-    CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_SH_GATE], l.w[DN_SQ_SH_UP], m->act, N, lc.shared_ff, W, false, ACT_CGLU,
+    CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_SH_GATE], l.w[DN_SQ_SH_UP], m->act, N, lc.shared_ff, W, false, eact,
                  LinMaps{wm(DN_SQ_SH_GATE), wm(DN_SQ_SH_UP), &m->x_h}, lc.shared_limit));
     CK(mark(m, DN_SEQ_PH_FF_DOWN, s));
     CK(linear<T>(m, s, (const T*)m->act, l.w[DN_SQ_SH_DOWN], nullptr, m->y2, N, W, lc.shared_ff, true, 0, LinMaps{wm(DN_SQ_SH_DOWN), nullptr, &l.x_act}));
   }
   CK(mark(m, DN_SEQ_PH_WRITE_BACK, s));
+  if (!combine) return DN_OK;
   CK(launch(k_moe_combine<T>, dim3((unsigned)(((size_t)N * W + 255) / 256)), dim3(256), 0, s, (const float*)m->eo, (const float*)m->rwt, (const int32_t*)m->rpos, N, W, top,
-            m->y, fused ? m->xs : (float*)nullptr, lc.shared_ff > 0 ? (const float*)m->y2 : (const float*)nullptr, w(DN_SQ_POST2), w(DN_SQ_POST2_B), w(DN_SQ_POST2_ALPHA), nx));
+            m->y, fused ? m->xs : (float*)nullptr, lc.shared_ff > 0 ? (const float*)m->y2 : (const float*)nullptr, w(DN_SQ_POST2), w(DN_SQ_POST2_B), w(DN_SQ_POST2_ALPHA), nx,
+            scored ? (const int32_t*)m->ridx : (const int32_t*)nullptr, E, (const T*)m->h, lc.shared_gate ? (const float*)m->sgate : (const float*)nullptr));
   return DN_OK;
 }
 
@@ -751,6 +804,7 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
   const int ew = (int)((NW + 255) / 256), ew4 = (int)((NW / 4 + 255) / 256);
   const dim3 nthr(W >= 4096 ? 512 : W >= 2048 ? 256 : 128);     // threads of a norm block: a function of the width only
   const bool dyt = c.norm_kind == DN_NORM_DYT;
+  const bool pre = !c.no_pre_norm;      // false: the sublayers read the residual itself, h = T(x)
   auto mwp = [&](int which) { return (const T*)m->mw[which - DN_SQ_EMBED]; };
   auto write_back = [&](const T* mix, const T* out) {
     if (W % 4 == 0) return launch(k_write_back<T, 4>, dim3(ew4), dim3(256), 0, s, m->xs, N, W, S, mix, out, (const float*)m->y);
@@ -760,13 +814,16 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
   const NextNorm<T> no_next{nullptr, nullptr, nullptr, nullptr};
   // the norm before the sublayer that follows, when the joining kernel can produce it (plain residual, both norms dynamic tanh)
   const bool can_fuse_next = c.post_norm && dyt && S <= 0;
-  bool h_ready = false;
   auto next_norm = [&](const SeqLayer& nl, int which) {
     return NextNorm<T>{(const T*)nl.w[which], (const T*)nl.w[which == DN_SQ_NORM1 ? DN_SQ_NORM1_B : DN_SQ_NORM2_B],
                        (const T*)nl.w[which == DN_SQ_NORM1 ? DN_SQ_NORM1_ALPHA : DN_SQ_NORM2_ALPHA], (T*)m->h};
   };
-  auto join = [&](SeqLayer& l, int post, int hc_mix, int hc_out, float a, const float* y2, float bb, NextNorm<T> nx) -> cudaError_t {
+  const MoeSrc<T> no_moe{nullptr, nullptr, nullptr, nullptr, 0, 0, nullptr, nullptr, nullptr};
+  auto join = [&](SeqLayer& l, int post, int hc_mix, int hc_out, float a, const float* y2, float bb, NextNorm<T> nx, const MoeSrc<T>* ms = nullptr) -> cudaError_t {
     auto w = [&](int i) { return (const T*)l.w[i]; };
+    if (c.post_norm && !dyt)      // RMS norm of the sublayer's output, added to the plain residual; h = T(x) for a model without norms before
+      return launch(k_rms_join<T>, dim3(N), nthr, nsm, s, m->xs, W, ms ? (const float*)nullptr : (const float*)m->y, a, y2, bb,
+                    ms ? *ms : no_moe, w(post), 1, c.eps, pre ? (T*)nullptr : (T*)m->h);
     if (c.post_norm) {
       if (S <= 0) return launch(k_dyt_add<T>, dim3(ew), dim3(256), 0, s, m->xs, NW, W, (const float*)m->y, a, y2, bb, w(post), w(post + 1), w(post + 2), nx);
       cudaError_t e = launch(k_dyt_inplace<T>, dim3(ew), dim3(256), 0, s, m->y, NW, W, a, y2, bb, w(post), w(post + 1), w(post + 2));
@@ -780,7 +837,8 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
 #define PH(id) CK(mark(m, id, s))
   PH(DN_SEQ_PH_EMBED);
   CK(launch(k_embed<T>, dim3(N), dim3(128), 0, s, (const T*)m->embed, b, c.embed_scale, W, S1, m->xs, mwp(DN_SQ_EMBED_NORM), mwp(DN_SQ_EMBED_NORM_B),
-            c.embed_norm ? mwp(DN_SQ_EMBED_NORM_ALPHA) : (const T*)nullptr, m->x0));
+            c.embed_norm ? mwp(DN_SQ_EMBED_NORM_ALPHA) : (const T*)nullptr, m->x0, pre ? (T*)nullptr : (T*)m->h));
+  bool h_ready = !pre;
   for (int ri = 0; ri < (int)m->runs.size(); ri++) {
     const Run& run = m->runs[ri];
     SeqLayer& l = m->L[run.layer];
@@ -795,7 +853,9 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
     }
     // ---- mixer sublayer
     PH(DN_SEQ_PH_NORM);
-    if (!h_ready || run.inject)
+    if (!pre) {
+      if (!h_ready || run.inject) CK(launch(k_cast<T>, dim3(ew), dim3(256), 0, s, (const float*)m->xs, NW, (T*)m->h));
+    } else if (!h_ready || run.inject)
       CK(launch(k_read_norm<T>, dim3(N), nthr, nsm, s, m->xs, N, W, S, w(DN_SQ_HC1_IN), w(DN_SQ_NORM1), dyt ? 0 : 1, 0, c.eps, (const int32_t*)nullptr, (T*)m->h,
                 w(DN_SQ_NORM1_B), dyt ? w(DN_SQ_NORM1_ALPHA) : (const T*)nullptr));
     h_ready = false;
@@ -835,7 +895,7 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
     }
     if (lc.mixer == DN_MIX_ATTENTION || lc.mixer == DN_MIX_PARALLEL) {
       AttnPrep a{lc.heads, lc.kv_heads, lc.dim, lc.vdim, lc.conv, lc.rot_dims, l.Ck ? 1 : 0, lc.qk_norm, c.eps, l.inv_freq};
-      AttnExtra ex{lc.softcap, lc.sink ? l.w[DN_SQ_SINK] : nullptr, lc.out_gate ? (const float*)m->pa : nullptr};
+      AttnExtra ex{lc.softcap, lc.sink ? l.w[DN_SQ_SINK] : nullptr, lc.out_gate ? (const float*)m->pa : nullptr, lc.mask_kind == DN_MASK_WINDOW ? 1 : 0, 0};
       const size_t sm = ((size_t)l.Cq + l.Ck + 40) * 4;
       PH(DN_SEQ_PH_ATTN_PREP);
       CK(launch(k_attn_prep<T>, dim3(N), dim3(256), sm, s, a, b, (const T*)m->uq, (const T*)m->uk, (const T*)m->uv, w(DN_SQ_Q_CONV),
@@ -847,11 +907,55 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
       else {
         // a small step (decode): long rows are split over up to AT_MAX_SPLITS blocks, joined by k_attn_merge
         const int Z = N <= AT_SPLIT_ROWS ? AT_MAX_SPLITS : 1;
-        CK(launch(k_attn<T>, dim3(N, lc.heads, Z), dim3(AT_WARPS * 32), (size_t)(((lc.dim + 3) & ~3) + AT_WARPS * (2 + (lc.vdim + 31) / 32 * 32)) * 4, s, b,
+        CK(launch(k_attn<T, 8>, dim3(N, lc.heads, Z), dim3(AT_WARPS * 32), (size_t)(((lc.dim + 3) & ~3) + AT_WARPS * (2 + (lc.vdim + 31) / 32 * 32)) * 4, s, b,
                   (const T*)m->qb, (const T*)m->kpool[run.kv_index],
                   (const T*)m->vpool[run.kv_index], lc.heads, lc.kv_heads, lc.dim, lc.vdim, lc.chunk, lc.scale, ex, (T*)m->mo, m->attn_part));
         if (Z > 1) CK(launch(k_attn_merge<T>, dim3(N, lc.heads), dim3(128), 0, s, b, lc.heads, lc.vdim, lc.chunk, Z, ex, (const float*)m->attn_part, (T*)m->mo));
       }
+    } else if (lc.mixer == DN_MIX_LATENT) {
+      // projections: q (or its latent, normed, then up), the key/value latent row, the heads' gates
+      const int R = lc.kv_rank, dr = lc.rot_part, dq = lc.dim + dr;
+      PH(DN_SEQ_PH_PROJ);
+      void* q1 = lc.q_rank > 0 ? m->lr : m->uq;
+      const int q1w = lc.q_rank > 0 ? lc.q_rank : l.Cq, q1t = lc.q_rank > 0 ? DN_SQ_DQ : DN_SQ_Q;
+      if (few) {
+        add(nullptr, q1t, q1, q1w, 0); add(nullptr, DN_SQ_DKV, m->uk, l.Ck, 0);
+        if (lc.out_gate) add(nullptr, DN_SQ_HEAD_GATE, m->pa, lc.heads, 1);
+        CK(run_segs());
+      } else {
+        CK(linear<T>(m, s, (const T*)m->h, l.w[q1t], nullptr, q1, N, q1w, W, false, 0, LinMaps{wm(q1t), nullptr, &m->x_h}));
+        CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_DKV], nullptr, m->uk, N, l.Ck, W, false, 0, LinMaps{wm(DN_SQ_DKV), nullptr, &m->x_h}));
+        if (lc.out_gate)
+          CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_HEAD_GATE], nullptr, m->pa, N, lc.heads, W, true, 0, LinMaps{wm(DN_SQ_HEAD_GATE), nullptr, &m->x_h}));
+      }
+      if (lc.q_rank > 0) {
+        CK(launch(k_rms_rows<T>, dim3(N), dim3(128), 0, s, (T*)m->lr, lc.q_rank, w(DN_SQ_DQ_NORM), c.eps));
+        CK(linear<T>(m, s, (const T*)m->lr, l.w[DN_SQ_Q], nullptr, m->uq, N, l.Cq, lc.q_rank, false, 0, LinMaps{wm(DN_SQ_Q), nullptr, &l.x_lr}));
+      }
+      PH(DN_SEQ_PH_ATTN_PREP);
+      LatentPrep a{lc.heads, lc.dim, dr, R, lc.rot_dims, lc.rot_layout == DN_ROT_HALF ? 1 : 0, c.eps, l.inv_freq};
+      T* pool = (T*)m->kpool[run.kv_index];
+      CK(launch(k_latent_prep<T>, dim3(N), dim3(256), 0, s, a, b, (const T*)m->uq, (const T*)m->uk, w(DN_SQ_DKV_NORM), (T*)m->qb, pool));
+      // the unrotated query parts into the latent space: qb[n, h, 0:R] = W_uk,h^T q[n, h, 0:dim]
+      CK(launch(k_linear_heads<T>, dim3((R + 63) / 64, (N + 63) / 64, lc.heads), dim3(256), 0, s, (const T*)m->uq, w(DN_SQ_UK), (T*)m->qb, N, R, lc.dim,
+                HeadsGeom{l.Cq, dq, l.Cql, l.Ck, (size_t)lc.dim * R, 1, R}));
+      // multi-query attention of all heads over the cached rows: keys [R + dr], values = their first R numbers
+      PH(DN_SEQ_PH_ATTN);
+      AttnExtra ex{lc.softcap, nullptr, lc.out_gate ? (const float*)m->pa : nullptr, lc.mask_kind == DN_MASK_WINDOW ? 1 : 0, l.Ck};
+      {
+        const int Z = N <= AT_SPLIT_ROWS ? AT_MAX_SPLITS : 1;
+        const size_t sm = (size_t)(((l.Ck + 3) & ~3) + AT_WARPS * (2 + (R + 31) / 32 * 32)) * 4;
+        if (R <= 256)
+          CK(launch(k_attn<T, 8>, dim3(N, lc.heads, Z), dim3(AT_WARPS * 32), sm, s, b, (const T*)m->qb, (const T*)pool, (const T*)pool, lc.heads, 1, l.Ck, R,
+                    lc.chunk, lc.scale, ex, (T*)m->gt, m->attn_part));
+        else
+          CK(launch(k_attn<T, 16>, dim3(N, lc.heads, Z), dim3(AT_WARPS * 32), sm, s, b, (const T*)m->qb, (const T*)pool, (const T*)pool, lc.heads, 1, l.Ck, R,
+                    lc.chunk, lc.scale, ex, (T*)m->gt, m->attn_part));
+        if (Z > 1) CK(launch(k_attn_merge<T>, dim3(N, lc.heads), dim3(128), 0, s, b, lc.heads, R, lc.chunk, Z, ex, (const float*)m->attn_part, (T*)m->gt));
+      }
+      // out of the latent space: mo[n, h, :] = W_uv,h gt[n, h, :]
+      CK(launch(k_linear_heads<T>, dim3((lc.vdim + 63) / 64, (N + 63) / 64, lc.heads), dim3(256), 0, s, (const T*)m->gt, w(DN_SQ_UV), (T*)m->mo, N, lc.vdim, R,
+                HeadsGeom{l.Col, R, l.Co, lc.vdim, (size_t)lc.vdim * R, R, 1}));
     } else if (lc.mixer == DN_MIX_DELTA) {
       if (!few) {
         CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_A], nullptr, m->pa, N, lc.heads, W, true, 0, LinMaps{wm(DN_SQ_A), nullptr, &m->x_h}));
@@ -946,27 +1050,37 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
     PH(DN_SEQ_PH_WRITE_BACK);
     const NextNorm<T> nx_mix = lc.ff > 0 ? (can_fuse_next ? next_norm(l, DN_SQ_NORM2) : no_next) : nx_run;
     CK(join(l, DN_SQ_POST1, DN_SQ_HC1_MIX, DN_SQ_HC1_OUT, ja, jy2, jb, nx_mix));
-    if (lc.ff == 0) h_ready = nx_run.alpha != nullptr;
+    if (lc.ff == 0) h_ready = nx_run.alpha != nullptr || !pre;
     // ---- feed-forward sublayer
     if (lc.ff > 0) {
       PH(DN_SEQ_PH_NORM);
-      if (!can_fuse_next)
+      if (!can_fuse_next && pre)
         CK(launch(k_read_norm<T>, dim3(N), nthr, nsm, s, m->xs, N, W, S, w(DN_SQ_HC2_IN), w(DN_SQ_NORM2), dyt ? 0 : 1, 0, c.eps, (const int32_t*)nullptr, (T*)m->h,
                   w(DN_SQ_NORM2_B), dyt ? w(DN_SQ_NORM2_ALPHA) : (const T*)nullptr));
       if (lc.mlp_kind == DN_MLP_MOE) {
         const bool fused = c.post_norm && S <= 0;
-        const int rc = moe_ff<T>(m, l, N, fused, fused ? nx_run : no_next, s);
+        const bool rmsj = fused && !dyt;      // the RMS join adds the pairs, the identity experts' input and the gated shared expert itself
+        const int rc = moe_ff<T>(m, l, N, fused, fused ? nx_run : no_next, s, !rmsj);
         if (rc != DN_OK) return rc;
-        if (!fused) CK(join(l, DN_SQ_POST2, DN_SQ_HC2_MIX, DN_SQ_HC2_OUT, 1.f, lc.shared_ff > 0 ? (const float*)m->y2 : nullptr, 1.f, nx_run));
-        h_ready = nx_run.alpha != nullptr;
+        if (rmsj) {
+          const bool scored = lc.router_kind == DN_ROUTER_SCORED;
+          const MoeSrc<T> ms{m->eo, m->rwt, m->rpos, m->ridx, lc.top, scored ? lc.experts : INT32_MAX, (const T*)m->h,
+                             lc.shared_ff > 0 ? (const float*)m->y2 : (const float*)nullptr, lc.shared_gate ? (const float*)m->sgate : (const float*)nullptr};
+          CK(join(l, DN_SQ_POST2, DN_SQ_HC2_MIX, DN_SQ_HC2_OUT, 1.f, nullptr, 0.f, no_next, &ms));
+        } else if (!fused) CK(join(l, DN_SQ_POST2, DN_SQ_HC2_MIX, DN_SQ_HC2_OUT, 1.f, lc.shared_ff > 0 ? (const float*)m->y2 : nullptr, 1.f, nx_run));
+        h_ready = nx_run.alpha != nullptr || !pre;
       } else {
         PH(DN_SEQ_PH_FF_UP);
-        CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_GATE], l.w[DN_SQ_UP], m->act, N, lc.ff, W, false, ACT_GEGLU, LinMaps{wm(DN_SQ_GATE), wm(DN_SQ_UP), &m->x_h}));
+        if (lc.ff_act == DN_FF_RELU2)      // no gate: relu(W_up h + b)^2
+          CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_UP], nullptr, m->act, N, lc.ff, W, false, ACT_RELU2, LinMaps{wm(DN_SQ_UP), nullptr, &m->x_h}, 0.f, l.w[DN_SQ_UP_B]));
+        else
+          CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_GATE], l.w[DN_SQ_UP], m->act, N, lc.ff, W, false, ACT_GEGLU, LinMaps{wm(DN_SQ_GATE), wm(DN_SQ_UP), &m->x_h}));
         PH(DN_SEQ_PH_FF_DOWN);
-        CK(linear<T>(m, s, (const T*)m->act, l.w[DN_SQ_DOWN], nullptr, m->y, N, W, lc.ff, true, 0, LinMaps{wm(DN_SQ_DOWN), nullptr, &l.x_act}));
+        CK(linear<T>(m, s, (const T*)m->act, l.w[DN_SQ_DOWN], nullptr, m->y, N, W, lc.ff, true, 0, LinMaps{wm(DN_SQ_DOWN), nullptr, &l.x_act}, 0.f,
+                     lc.ff_act == DN_FF_RELU2 ? l.w[DN_SQ_DOWN_B] : nullptr));
         PH(DN_SEQ_PH_WRITE_BACK);
         CK(join(l, DN_SQ_POST2, DN_SQ_HC2_MIX, DN_SQ_HC2_OUT, 1.f, nullptr, 0.f, nx_run));
-        h_ready = nx_run.alpha != nullptr && c.post_norm && S <= 0;
+        h_ready = (nx_run.alpha != nullptr && c.post_norm && S <= 0) || !pre;
       }
     }
     PH(DN_SEQ_PH_OTHER);
@@ -1019,16 +1133,20 @@ extern "C" int dn_seq_step(dn_seq_model* m, int E, const int32_t* slots, const i
     auto has = [&](int k) { return l.w[k] != nullptr; };
     const int mx = l.c.mixer;
     const bool moe = l.c.mlp_kind == DN_MLP_MOE;
-    bool ok = has(DN_SQ_NORM1) && has(DN_SQ_Q) && has(DN_SQ_O) && (l.c.ff == 0 || has(DN_SQ_NORM2));
-    if (l.c.ff > 0 && !moe) ok = ok && has(DN_SQ_GATE) && has(DN_SQ_UP) && has(DN_SQ_DOWN);
+    bool ok = has(DN_SQ_Q) && has(DN_SQ_O);
+    if (!m->cfg.no_pre_norm) ok = ok && has(DN_SQ_NORM1) && (l.c.ff == 0 || has(DN_SQ_NORM2));
+    if (l.c.ff > 0 && !moe) ok = ok && (l.c.ff_act == DN_FF_RELU2 || has(DN_SQ_GATE)) && has(DN_SQ_UP) && has(DN_SQ_DOWN);
     if (l.c.ff > 0 && moe) {
       ok = ok && has(DN_SQ_ROUTER) && (l.c.shared_ff == 0 || (has(DN_SQ_SH_GATE) && has(DN_SQ_SH_UP) && has(DN_SQ_SH_DOWN)));
+      if (l.c.shared_gate) ok = ok && has(DN_SQ_SH_SG);
       for (const void* p : l.etab_h) ok = ok && p != nullptr;
     }
     if (dyt) ok = ok && has(DN_SQ_NORM1_B) && has(DN_SQ_NORM1_ALPHA) && (l.c.ff == 0 || (has(DN_SQ_NORM2_B) && has(DN_SQ_NORM2_ALPHA)));
-    if (m->cfg.post_norm) ok = ok && has(DN_SQ_POST1) && has(DN_SQ_POST1_B) && has(DN_SQ_POST1_ALPHA) &&
-                               (l.c.ff == 0 || (has(DN_SQ_POST2) && has(DN_SQ_POST2_B) && has(DN_SQ_POST2_ALPHA)));
-    if (l.Ck) ok = ok && has(DN_SQ_K) && has(DN_SQ_V);
+    if (m->cfg.post_norm) ok = ok && has(DN_SQ_POST1) && (l.c.ff == 0 || has(DN_SQ_POST2));
+    if (m->cfg.post_norm && dyt) ok = ok && has(DN_SQ_POST1_B) && has(DN_SQ_POST1_ALPHA) && (l.c.ff == 0 || (has(DN_SQ_POST2_B) && has(DN_SQ_POST2_ALPHA)));
+    if (mx == DN_MIX_LATENT) ok = ok && has(DN_SQ_DKV) && has(DN_SQ_DKV_NORM) && has(DN_SQ_UK) && has(DN_SQ_UV) && (!l.c.out_gate || has(DN_SQ_HEAD_GATE)) &&
+                                  (l.c.q_rank == 0 || (has(DN_SQ_DQ) && has(DN_SQ_DQ_NORM)));
+    else if (l.Ck) ok = ok && has(DN_SQ_K) && has(DN_SQ_V);
     if (l.c.conv > 0) ok = ok && has(DN_SQ_Q_CONV) && (!l.Ck || (has(DN_SQ_K_CONV) && has(DN_SQ_V_CONV)));
     if (mx == DN_MIX_ATTENTION || mx == DN_MIX_PARALLEL) {
       if (l.c.qk_norm) ok = ok && has(DN_SQ_Q_NORM) && (!l.Ck || has(DN_SQ_K_NORM));

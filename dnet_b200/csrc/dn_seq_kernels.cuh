@@ -17,7 +17,10 @@
 //   * gated delta rule: per head a [dk, dv] fp32 state with decay, delta-rule write and read-out
 //   * dynamic-tanh norm (no statistics), capped scores, a sink term in the softmax denominator, per-head output gates
 //   * (dn_seq_recur.cuh) decayed outer-product recurrences with a decay per key channel, token-shift mixing
-//   * (dn_seq_moe.cuh) routed clamped-GLU experts
+//   * (dn_seq_moe.cuh) routed GLU experts, chosen by logits or by corrected, group-limited softmax scores
+//   * (dn_seq_latent.cuh) latent attention: one compressed row per token in the cache, queries absorbed into it
+//   * a sliding-window mask beside the block mask; rotary pairs interleaved or half apart
+//   * RMS norm on a sublayer's output only (the sublayers read the residual itself)
 // T is the storage type of weights and activations (bf16 or float); sums, norms, scores, positions, gates and
 // states are fp32 in both.
 #pragma once
@@ -75,13 +78,16 @@ __device__ __forceinline__ float clamped_glu_f(float g, float u, float limit) {
   u = fminf(fmaxf(u, -limit), limit);
   return g * sigmoid_f(1.702f * g) * (u + 1.f);
 }
-// activation of a product's epilogue: 0 none; 1 gelu_tanh(a) * b; 2 tanh(a); 3 clamped GLU of (a, b) with `lim`
-constexpr int ACT_NONE = 0, ACT_GEGLU = 1, ACT_TANH = 2, ACT_CGLU = 3;
-__device__ __forceinline__ bool act_two(int act) { return act == ACT_GEGLU || act == ACT_CGLU; }
+// activation of a product's epilogue: 0 none; 1 gelu_tanh(a) * b; 2 tanh(a); 3 clamped GLU of (a, b) with `lim`;
+// 4 silu(a) * b; 5 relu(a)^2.  A bias, where a product has one, is added to a before the activation.
+constexpr int ACT_NONE = 0, ACT_GEGLU = 1, ACT_TANH = 2, ACT_CGLU = 3, ACT_SWIGLU = 4, ACT_RELU2 = 5;
+__host__ __device__ __forceinline__ bool act_two(int act) { return act == ACT_GEGLU || act == ACT_CGLU || act == ACT_SWIGLU; }
 __device__ __forceinline__ float act_apply(int act, float a, float b, float lim) {
   if (act == ACT_GEGLU) return gelu_tanh_f(a) * b;
   if (act == ACT_TANH) return tanhf(a);
   if (act == ACT_CGLU) return clamped_glu_f(a, b, lim);
+  if (act == ACT_SWIGLU) return silu_f(a) * b;
+  if (act == ACT_RELU2) { const float r = fmaxf(a, 0.f); return r * r; }
   return a;
 }
 // sum += v with the rounding error of the addition carried in c (compensated summation)
@@ -112,10 +118,11 @@ struct Batch {
 
 // ---------------------------------------------------------------------------------------------------------------
 // embedding -> residual streams
-// nalpha != null: the embedding is dynamic-tanh normed; x0 != null: it is also kept aside (the loop's injection reads it)
+// nalpha != null: the embedding is dynamic-tanh normed; x0 != null: it is also kept aside (the loop's injection reads it);
+// hout != null: also in the products' number format (models whose sublayers read the residual without a norm)
 template <class T>
 __global__ void k_embed(const T* __restrict__ embed, Batch b, float scale, int W, int S1, float* __restrict__ xs, const T* __restrict__ nw,
-                        const T* __restrict__ nb, const T* __restrict__ nalpha, float* __restrict__ x0) {
+                        const T* __restrict__ nb, const T* __restrict__ nalpha, float* __restrict__ x0, T* __restrict__ hout) {
   const int n = blockIdx.x;
   const size_t row = (size_t)b.tok[n] * W;
   const float alpha = nalpha ? ldf(nalpha) : 0.f;
@@ -124,6 +131,7 @@ __global__ void k_embed(const T* __restrict__ embed, Batch b, float scale, int W
     if (nalpha) v = dyt_f(v, alpha, nw, nb, c);
     for (int s = 0; s < S1; s++) xs[((size_t)s * b.N + n) * W + c] = v;
     if (x0) x0[(size_t)n * W + c] = v;
+    if (hout) stf(hout + (size_t)n * W + c, v);      // the first sublayer reads the residual itself
   }
 }
 
@@ -269,6 +277,60 @@ __global__ void k_softcap(float* __restrict__ z, size_t n, float cap) {
   if (i < n) z[i] = cap * tanhf(z[i] / cap);
 }
 
+// h <- T(x): the input of a sublayer that reads the residual itself
+template <class T>
+__global__ void k_cast(const float* __restrict__ x, size_t n, T* __restrict__ h) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) stf(h + i, x[i]);
+}
+
+// A sublayer's output joins the plain residual through an RMS norm of its own:
+//   v = a y + b y2 + sum_j wt[j] (expert output j | the token's input, for an identity expert) + gate sh      (all optional)
+//   x <- x + v / sqrt(mean(v^2) + eps) * (w or 1 + w);   hout <- T(x), the input of the sublayer that follows
+// One block per token; a thread's partial sum of squares runs over its own columns in ascending order and the block adds
+// the partials by index, so a row's result depends on W and the block size only.
+template <class T>
+struct MoeSrc {
+  const float* eo;          // [pairs, W] expert outputs (null: no routed part)
+  const float* wt;          // [N, top]
+  const int32_t* pos;       // [N, top] row of a pair in eo
+  const int32_t* idx;       // [N, top] chosen expert; >= E: an identity expert
+  int top, E;
+  const T* hid;             // [N, W] the feed-forward's input
+  const float* sh;          // [N, W] the shared expert's output (null: none)
+  const float* sgate;       // [N] its gate, already through the sigmoid (null: 1)
+};
+template <class T>
+__global__ void k_rms_join(float* __restrict__ x, int W, const float* __restrict__ y, float a, const float* __restrict__ y2, float b, MoeSrc<T> ms,
+                           const T* __restrict__ nw, int one_plus, float eps, T* __restrict__ hout) {
+  extern __shared__ __align__(16) float sm[];
+  float* v = sm;            // [W]
+  float* red = sm + W;      // [33]
+  const size_t n = blockIdx.x, base = n * W;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    float u = y ? a * y[base + c] : 0.f;
+    if (y2) u += b * y2[base + c];
+    if (ms.eo) {
+      for (int j = 0; j < ms.top; j++) {
+        const int e = ms.idx[n * ms.top + j];
+        const float src = e < ms.E ? ms.eo[(size_t)ms.pos[n * ms.top + j] * W + c] : ldf(ms.hid + base + c);
+        u = fmaf(ms.wt[n * ms.top + j], src, u);
+      }
+    }
+    if (ms.sh) u = fmaf(ms.sgate ? ms.sgate[n] : 1.f, ms.sh[base + c], u);
+    v[c] = u;
+    ss += u * u;
+  }
+  ss = block_sum(ss, red);
+  const float rinv = 1.f / sqrtf(ss / (float)W + eps);
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    const float xn = x[base + c] + v[c] * rinv * (ldf(nw + c) + (one_plus ? 1.f : 0.f));
+    x[base + c] = xn;
+    if (hout) stf(hout + base + c, xn);
+  }
+}
+
 // sum of the streams (inspection hook)
 __global__ void k_stream_sum(const float* __restrict__ xs, int N, int W, int S1, float* __restrict__ o) {
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -286,7 +348,8 @@ __global__ void k_stream_sum(const float* __restrict__ xs, int N, int W, int S1,
 // OUT32: write fp32 (residual-side outputs), else T.  act: ACT_* (the two-operand ones read W2 as well).
 template <class T, bool OUT32>
 __global__ void __launch_bounds__(256) k_linear(const T* __restrict__ X, const T* __restrict__ Wt, const T* __restrict__ W2,
-                                                void* __restrict__ Y, int N, int O, int K, int act, float alim) {
+                                                void* __restrict__ Y, int N, int O, int K, int act, float alim,
+                                                const T* __restrict__ bias) {
   const bool two = act_two(act);
   constexpr int BM = 64, BN = 64, BK = 16;
   __shared__ float Xs[BK][BM + 4], Ws[BK][BN + 4], Vs[BK][BN + 4];
@@ -347,7 +410,7 @@ __global__ void __launch_bounds__(256) k_linear(const T* __restrict__ X, const T
     for (int j = 0; j < 4; j++) {
       const int o = o0 + tx * 4 + j;
       if (o >= O) continue;
-      const float v = act_apply(act, acc[i][j], acc2[i][j], alim);
+      const float v = act_apply(act, acc[i][j] + (bias ? ldf(bias + o) : 0.f), acc2[i][j], alim);
       if (OUT32) ((float*)Y)[(size_t)n * O + o] = v;
       else stf((T*)Y + (size_t)n * O + o, v);
     }
@@ -361,7 +424,8 @@ template <class T> struct Vec16 { static constexpr int n = 16 / sizeof(T); };
 // one warp, one output feature o of one product
 template <class T>
 __device__ __forceinline__ void linear_row(const T* __restrict__ X, const T* __restrict__ Wt, const T* __restrict__ W2, void* __restrict__ Y,
-                                           bool out32, int N, int O, int K, int actc, int o, float alim = 0.f) {
+                                           bool out32, int N, int O, int K, int actc, int o, float alim = 0.f,
+                                           const T* __restrict__ bias = nullptr) {
   constexpr int V = Vec16<T>::n;
   const bool act = act_two(actc);
   const int lane = threadIdx.x & 31;
@@ -405,7 +469,7 @@ __device__ __forceinline__ void linear_row(const T* __restrict__ X, const T* __r
 #pragma unroll
   for (int i = 0; i < 8; i++) {
     if (i < N) {
-      float v = warp_sum(acc[i]);
+      float v = warp_sum(acc[i]) + (bias ? ldf(bias + o) : 0.f);
       v = act_apply(actc, v, act ? warp_sum(acc2[i]) : 0.f, alim);
       if (lane == 0) {
         if (out32) ((float*)Y)[(size_t)i * O + o] = v;
@@ -416,10 +480,11 @@ __device__ __forceinline__ void linear_row(const T* __restrict__ X, const T* __r
 }
 template <class T, bool OUT32>
 __global__ void __launch_bounds__(256) k_linear_rows(const T* __restrict__ X, const T* __restrict__ Wt, const T* __restrict__ W2,
-                                                     void* __restrict__ Y, int N, int O, int K, int act, float alim) {
+                                                     void* __restrict__ Y, int N, int O, int K, int act, float alim,
+                                                     const T* __restrict__ bias) {
   const int o = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (o >= O) return;
-  linear_row<T>(X, Wt, W2, Y, OUT32, N, O, K, act, o, alim);
+  linear_row<T>(X, Wt, W2, Y, OUT32, N, O, K, act, o, alim, bias);
 }
 // several products of the same few rows in one launch (the projections of a mixer in a decode step): blocks are
 // dealt to the products in order, 8 output features each
@@ -579,7 +644,14 @@ struct AttnExtra {
   float softcap;
   const void* sink;
   const float* gate;
+  int window;      // 1: `chunk` is a sliding window -- a query at p sees the keys p - chunk + 1 .. p
+  int v_ld;        // row stride of the value pool in elements (0: G dv); latent attention reads its values out of the key rows
 };
+// first key a query at position p sees
+__device__ __forceinline__ int attn_lo(int p, int chunk, int window) {
+  if (chunk <= 0) return 0;
+  return window ? max(0, p - chunk + 1) : (p / chunk) * chunk;
+}
 // Long rows of a small step are split over gridDim.z blocks: a row that sees n keys uses ceil(n / AT_SPLIT_KEYS) of
 // them (at most gridDim.z), split z taking every nz-th group of AT_WARPS tiles; each writes its partial (maximum,
 // sum, output) to scratch and k_attn_merge joins them in the order of z.  The split depends on the row's own
@@ -610,7 +682,7 @@ __device__ __forceinline__ void ld_vals(float (&v)[8], const T* p, int cnt, bool
 #pragma unroll
   for (int i = 0; i < 8; i++) if (i < cnt) v[i] = ldf(p + i);
 }
-template <class T>
+template <class T, int MAXV>      // MAXV: value dims a lane owns at most (8: dv <= 256, 16: dv <= 512)
 __global__ void __launch_bounds__(AT_WARPS * 32) k_attn(Batch b, const T* __restrict__ q, const T* __restrict__ kpool,
                                                         const T* __restrict__ vpool, int H, int G, int dk, int dv, int chunk, float scale,
                                                         AttnExtra ex, T* __restrict__ out, float* __restrict__ part_g) {
@@ -621,19 +693,19 @@ __global__ void __launch_bounds__(AT_WARPS * 32) k_attn(Batch b, const T* __rest
   float* part = sm + ((dk + 3) & ~3);               // [AT_WARPS][2 + dvp]
   const int n = blockIdx.x, h = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = h / (H / G), slot = b.slot[n], p = b.pos[n];
-  const int lo = chunk > 0 ? (p / chunk) * chunk : 0;
+  const int lo = attn_lo(p, chunk, ex.window);
   const int nz = attn_splits(p - lo + 1, (int)gridDim.z), z = blockIdx.z;
   if (z >= nz) return;
-  const int Ck = G * dk, Cv = G * dv;
+  const int Ck = G * dk, Cv = ex.v_ld > 0 ? ex.v_ld : G * dv;
   for (int d = threadIdx.x; d < dk; d += blockDim.x) qs[d] = ldf(q + ((size_t)n * H + h) * dk + d);
   __syncthreads();
   const int32_t* bt = b.bt + (size_t)slot * b.max_pages;
   const bool kvec = (dk % V) == 0;                  // K rows start on 16-byte boundaries
   const int vcnt = min(VPL, max(0, dv - lane * VPL));
-  const bool vvec = (dv % 32) == 0;
-  float m = -INFINITY, l = 0.f, acc[8];
+  const bool vvec = (dv % 32) == 0 && ((size_t)Cv * sizeof(T)) % 16 == 0;
+  float m = -INFINITY, l = 0.f, acc[MAXV];
 #pragma unroll
-  for (int i = 0; i < 8; i++) acc[i] = 0.f;
+  for (int i = 0; i < MAXV; i++) acc[i] = 0.f;
   for (int j0 = lo + (z * AT_WARPS + warp) * 32; j0 <= p; j0 += nz * AT_WARPS * 32) {
     const int j = j0 + lane;
     float s = -INFINITY;
@@ -658,25 +730,30 @@ __global__ void __launch_bounds__(AT_WARPS * 32) k_attn(Batch b, const T* __rest
     const float pj = j <= p ? expf(s - mn) : 0.f;
     l = l * corr + warp_sum(pj);
 #pragma unroll
-    for (int i = 0; i < 8; i++) acc[i] *= corr;
+    for (int i = 0; i < MAXV; i++) acc[i] *= corr;
     const int cnt = min(32, p - j0 + 1);
 #pragma unroll 4
     for (int t = 0; t < cnt; t++) {
       const float pt = __shfl_sync(0xffffffffu, pj, t);
       const int jj = j0 + t;
       const T* vr = vpool + ((size_t)bt[jj / PAGE] * PAGE + (jj % PAGE)) * Cv + g * dv + lane * VPL;
-      float vv[8];
-      ld_vals(vv, vr, vcnt, vvec);
 #pragma unroll
-      for (int i = 0; i < 8; i++)
-        if (i < vcnt) acc[i] = fmaf(pt, vv[i], acc[i]);
+      for (int i0 = 0; i0 < MAXV; i0 += 8) {
+        if (i0 < vcnt) {
+          float vv[8];
+          ld_vals(vv, vr + i0, min(8, vcnt - i0), vvec);
+#pragma unroll
+          for (int i = 0; i < 8; i++)
+            if (i0 + i < vcnt) acc[i0 + i] = fmaf(pt, vv[i], acc[i0 + i]);
+        }
+      }
     }
     m = mn;
   }
   float* mine = part + (size_t)warp * (2 + dvp);
   if (lane == 0) { mine[0] = m; mine[1] = l; }
 #pragma unroll
-  for (int i = 0; i < 8; i++)
+  for (int i = 0; i < MAXV; i++)
     if (i < VPL) mine[2 + lane * VPL + i] = acc[i];
   __syncthreads();
   const bool split = nz > 1;      // the sink and the gate then wait for the merge
@@ -703,7 +780,7 @@ __global__ void __launch_bounds__(AT_WARPS * 32) k_attn(Batch b, const T* __rest
 template <class T>
 __global__ void k_attn_merge(Batch b, int H, int dv, int chunk, int zmax, AttnExtra ex, const float* __restrict__ part_g, T* __restrict__ out) {
   const int n = blockIdx.x, h = blockIdx.y, p = b.pos[n];
-  const int lo = chunk > 0 ? (p / chunk) * chunk : 0;
+  const int lo = attn_lo(p, chunk, ex.window);
   const int nz = attn_splits(p - lo + 1, zmax);
   if (nz <= 1) return;
   const int dvp = (dv + 31) / 32 * 32;
@@ -784,14 +861,14 @@ __global__ void __launch_bounds__(128) k_attn_tiles(Batch b, const bf16* __restr
   const int s0 = b.ent_start[e] + t * AT_ROWS, s1 = b.ent_start[e + 1];
   const int rows = min(AT_ROWS, s1 - s0);
   const int p_first = b.ent_pos0[e] + t * AT_ROWS, p_last = p_first + rows - 1;
-  const int Ck = G * dk, Cv = G * dv;
+  const int Ck = G * dk, Cv = ex.v_ld > 0 ? ex.v_ld : G * dv;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   load_tile64<LQ>(Qs, q + ((size_t)s0 * H + h) * dk, (size_t)H * dk, dk, rows);
   __syncthreads();
   // this thread's two rows of its warp's 16
   const int r0 = warp * 16 + (lane >> 2), r1 = r0 + 8;
   const int p0 = r0 < rows ? p_first + r0 : -1, p1 = r1 < rows ? p_first + r1 : -1;
-  const int lo0 = (chunk > 0 && p0 >= 0) ? (p0 / chunk) * chunk : 0, lo1 = (chunk > 0 && p1 >= 0) ? (p1 / chunk) * chunk : 0;
+  const int lo0 = p0 >= 0 ? attn_lo(p0, chunk, ex.window) : 0, lo1 = p1 >= 0 ? attn_lo(p1, chunk, ex.window) : 0;
   const bool warp_live = warp * 16 < rows;
   uint32_t qf[DKP / 16][4];
 #pragma unroll
@@ -801,7 +878,7 @@ __global__ void __launch_bounds__(128) k_attn_tiles(Batch b, const bf16* __restr
   for (int j = 0; j < DVP / 8; j++) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
   const int32_t* bt = b.bt + (size_t)b.ent_slot[e] * b.max_pages;
-  const int lo_tile = chunk > 0 ? (p_first / chunk) * chunk : 0;
+  const int lo_tile = attn_lo(p_first, chunk, ex.window);
   for (int j0 = (lo_tile / PAGE) * PAGE; j0 <= p_last; j0 += PAGE) {
     const size_t prow = (size_t)bt[j0 / PAGE] * PAGE;
     const int kvalid = min(PAGE, p_last - j0 + 1);      // rows of the page beyond the last query's position are not read

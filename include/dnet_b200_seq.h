@@ -1,8 +1,9 @@
 /*
  * dnet_b200_seq.h -- C ABI of libdnet_b200_seq.so: the batched step of decoder models whose layers are a
- * sequence mixer (softmax attention over a paged cache -- block-masked, capped, with a sink and head gates --, a gated
- * delta-rule recurrence, decayed outer-product recurrences, or attention beside one of those) plus an optional gated or
- * routed feed-forward, tied together by S residual streams; a span of layers may run several times on the same weights.
+ * sequence mixer (softmax attention over a paged cache -- block-masked or sliding-window, capped, with a sink and head
+ * gates --, latent attention that caches one compressed row per token, a gated delta-rule recurrence, decayed
+ * outer-product recurrences, or attention beside one of those) plus an optional dense, gated or routed feed-forward,
+ * tied together by S residual streams; a span of layers may run several times on the same weights.
  *
  * Same conventions as dnet_b200.h: plain C, opaque handles, 0 or a negative DN_E* code, dn_seq_last_error() for
  * the text, caller-owned streams and buffers, weights BORROWED by pointer.  One handle serves one compute thread.
@@ -27,12 +28,29 @@ extern "C" {
 #define DN_MIX_DELTA 1
 #define DN_MIX_PARALLEL 2   /* softmax attention and a gated linear attention side by side on the same input */
 #define DN_MIX_WKV 3        /* token-shift mixing + a decayed outer-product state read with a bonus for the current token */
+#define DN_MIX_LATENT 4     /* latent attention: keys and values are up-projections of one cached latent row per token */
+
+#define DN_MASK_BLOCK 0     /* a query sees its own block of `chunk` positions, causally */
+#define DN_MASK_WINDOW 1    /* a query sees itself and the `chunk` - 1 positions before it */
+
+#define DN_ROT_INTERLEAVED 0   /* rotary pairs (2i, 2i + 1) */
+#define DN_ROT_HALF 1          /* rotary pairs (i, i + dims / 2) */
 
 #define DN_NORM_RMS 0       /* x / sqrt(mean(x^2) + eps) * w  (or 1 + w) */
 #define DN_NORM_DYT 1       /* tanh(alpha x) * w + b, elementwise */
 
-#define DN_MLP_DENSE 0      /* gelu_tanh(gate) * up -> down */
-#define DN_MLP_MOE 1        /* routed clamped-GLU experts (+ an optional shared one) */
+#define DN_MLP_DENSE 0      /* gelu_tanh(gate) * up -> down, or (ff_act) an ungated activation between up and down */
+#define DN_MLP_MOE 1        /* routed GLU experts (+ an optional shared one) */
+
+#define DN_FF_GEGLU 0       /* dense feed-forward: gelu_tanh(W_gate h) * (W_up h) */
+#define DN_FF_RELU2 1       /* dense feed-forward: relu(W_up h + b)^2, no gate; up and down may carry biases */
+
+#define DN_ROUTER_TOPK 0    /* the `top` largest logits choose; softmax over the chosen logits weighs */
+#define DN_ROUTER_SCORED 1  /* softmax over all experts scores; a correction is added for the choice only; experts form groups of
+                               which the best are kept; weights = chosen scores / their sum * router_scale */
+
+#define DN_EXPERT_CGLU 0    /* clamped GLU: g = min(gate, limit), u = clamp(up, +-limit), g sigmoid(1.702 g) (u + 1) */
+#define DN_EXPERT_SWIGLU 1  /* silu(gate) * up */
 
 typedef struct dn_seq_model dn_seq_model;
 typedef void* dn_seq_stream;   /* cudaStream_t */
@@ -66,6 +84,20 @@ typedef struct dn_seq_layer_cfg {
   float limit;         /* clamped GLU: gate <= limit, |up| <= limit */
   int32_t shared_ff;   /* width of the shared expert (0: none) */
   float shared_limit;
+  /* attention */
+  int32_t mask_kind;   /* DN_MASK_*: what `chunk` means */
+  int32_t rot_layout;  /* DN_ROT_* */
+  /* DN_MIX_LATENT: per head `dim` unrotated and `rot_part` rotated query / key dims (of which the first rot_dims turn),
+   * values of vdim; the cache holds kv_rank + rot_part numbers a token.  q_rank > 0: queries go through a normed latent too */
+  int32_t kv_rank, q_rank, rot_part;
+  /* feed-forward */
+  int32_t ff_act;      /* DN_FF_*: dense feed-forward */
+  int32_t router_kind; /* DN_ROUTER_* */
+  int32_t expert_act;  /* DN_EXPERT_*: routed and shared experts */
+  int32_t identity;    /* DN_ROUTER_SCORED: the router's last `identity` outputs stand for experts that return their input */
+  int32_t groups, groups_keep;   /* DN_ROUTER_SCORED: experts (identity ones included) in `groups` equal runs, the best kept (0: no groups) */
+  float router_scale;
+  int32_t shared_gate; /* 1: the shared expert's output is multiplied by sigmoid(w . h), one number a token */
 } dn_seq_layer_cfg;
 
 typedef struct dn_seq_cfg {
@@ -84,6 +116,7 @@ typedef struct dn_seq_cfg {
   /* layers loop_start .. loop_stop-1 run loop_times times in a row on the same weights, every pass with its own cache and
    * state; before the first layer of each pass x <- W_in [x; x0] with x0 the embedding's output.  loop_times = 0: no loop */
   int32_t loop_start, loop_stop, loop_times;
+  int32_t no_pre_norm;       /* 1: sublayers read the residual itself; only their outputs are normed (post_norm) */
 } dn_seq_cfg;
 
 /* tensors of a layer (dn_seq_bind: layer >= 0) and of the model (layer = -1) */
@@ -106,6 +139,11 @@ enum {
   DN_SQ_MU_R, DN_SQ_MU_K, DN_SQ_MU_V, DN_SQ_MU_G, DN_SQ_MU_W, DN_SQ_BONUS,
   /* DN_MLP_MOE: router [E, W] and its bias [E]; the shared expert */
   DN_SQ_ROUTER, DN_SQ_ROUTER_B, DN_SQ_SH_GATE, DN_SQ_SH_UP, DN_SQ_SH_DOWN,
+  /* DN_MIX_LATENT: query latent [q_rank, W] and its norm [q_rank] (DN_SQ_Q is then [H (dim + rot_part), q_rank]); key/value
+   * latent [kv_rank + rot_part, W] and its norm [kv_rank]; up-projections to keys [H dim, kv_rank] and values [H vdim, kv_rank] */
+  DN_SQ_DQ, DN_SQ_DQ_NORM, DN_SQ_DKV, DN_SQ_DKV_NORM, DN_SQ_UK, DN_SQ_UV,
+  /* biases of a dense feed-forward [ff], [W]; DN_ROUTER_SCORED: correction [experts + identity]; the shared expert's gate [W] */
+  DN_SQ_UP_B, DN_SQ_DOWN_B, DN_SQ_ROUTER_CORR, DN_SQ_SH_SG,
   DN_SQ_COUNT,
   DN_SQ_EMBED = 100, DN_SQ_FINAL_NORM, DN_SQ_HEAD, DN_SQ_FINAL_NORM_B, DN_SQ_FINAL_NORM_ALPHA,
   DN_SQ_EMBED_NORM, DN_SQ_EMBED_NORM_B, DN_SQ_EMBED_NORM_ALPHA, DN_SQ_LOOP_IN
