@@ -702,7 +702,8 @@ __global__ void __launch_bounds__(AT_WARPS * 32) k_attn(Batch b, const T* __rest
   const int32_t* bt = b.bt + (size_t)slot * b.max_pages;
   const bool kvec = (dk % V) == 0;                  // K rows start on 16-byte boundaries
   const int vcnt = min(VPL, max(0, dv - lane * VPL));
-  const bool vvec = (dv % 32) == 0 && ((size_t)Cv * sizeof(T)) % 16 == 0;
+  // 8- or 16-byte value loads: a lane's run of VPL numbers must start on such a boundary in every row
+  const bool vvec = (dv % 32) == 0 && ((size_t)Cv * sizeof(T)) % 16 == 0 && ((VPL * sizeof(T)) % 16 == 0 || VPL * sizeof(T) == 8);
   float m = -INFINITY, l = 0.f, acc[MAXV];
 #pragma unroll
   for (int i = 0; i < MAXV; i++) acc[i] = 0.f;

@@ -2,6 +2,8 @@
 own mechanisms against independent formulations, and the batcher's token loop over a fake model."""
 from __future__ import annotations
 
+import math
+
 import pytest
 import torch
 
@@ -61,7 +63,8 @@ def test_header_and_binding_agree():
     assert len(order) == len(_seqabi.LAYER_SLOT)
     spell = {"OUT_NORM": "mix.norm", "NORM1": "norm1", "NORM2": "norm2", "GATE": "mlp.gate", "UP": "mlp.up", "DOWN": "mlp.down",
              "HEAD_GATE": "head_gate", "SINK": "sink", "BONUS": "bonus", "DECAY1": "decay1", "DECAY2": "decay2", "DECAY_B": "decay.b",
-             "ROUTER": "router", "ROUTER_B": "router.b", "SH_GATE": "shared.gate", "SH_UP": "shared.up", "SH_DOWN": "shared.down"}
+             "ROUTER": "router", "ROUTER_B": "router.b", "SH_GATE": "shared.gate", "SH_UP": "shared.up", "SH_DOWN": "shared.down",
+             "UP_B": "mlp.up.b", "DOWN_B": "mlp.down.b", "ROUTER_CORR": "router.corr", "SH_SG": "shared.sg"}
     for i, name in enumerate(order):
         n = name[len("DN_SQ_"):]
         if n in spell:
@@ -124,6 +127,100 @@ def test_filinex_config_and_checkpoint_names():
     for k in want:
         if _LAYER_KEY.match(k) and ".mlp.e" not in k:
             assert k.split(".", 1)[1] in _seqabi.LAYER_SLOT, k
+
+
+def _lutesun_cfg():
+    moe = {"kind": "moe", "router": {"experts": 6, "top": 2, "identity": 2, "scale": 1.5, "groups": {"count": 4, "keep": 3}}, "expert": {"ff": 24},
+           "shared": {"ff": 16}}
+    mx = {"heads": 3, "dim": 10, "rot_dim": 6, "vdim": 7, "kv_rank": 20, "scale": 0.3, "rot": {"base": 777.0, "dims": 6}, "mask": {"size": 9}}
+    return {"architecture": "Lutesun", "vocab": 50, "width": 32, "norm": {"eps": 1e-5}, "embedding": {"scale": 0.25},
+            "layers": [{"type": "latent_attention", "mixer": mx, "mlp": {"kind": "dense", "ff": 40}},
+                       {"type": "latent_attention_2", "mixer": {**mx, "q_rank": 12, "heads": 2}, "mlp": moe},
+                       {"type": "latent_attention", "mixer": {**mx, "mask": None}, "mlp": {**moe, "shared": None, "router": {"experts": 4, "top": 1}}},
+                       {"type": "latent_attention_2", "mixer": {k: v for k, v in mx.items() if k != "q_rank"}, "mlp": None}]}
+
+
+def test_lutesun_config_and_checkpoint_names():
+    """every constant of the config lands in the structs, what the design fixes comes from the family, a size the config
+    lacks comes from a tensor's shape, and every tensor the oracle writes finds its place through the aliases"""
+    from dnet_b200 import _seqabi
+    from dnet_b200.core.models import ring_model_class
+    from dnet_b200.core.models.seqmix import _LAYER_KEY, parse_layer_list
+    from oracle import lutesun_oracle as lo
+
+    cfg = _lutesun_cfg()
+    cls = ring_model_class("lutesun")
+    with_rank = {**cfg, "layers": cfg["layers"][:3] + [{**cfg["layers"][3], "mixer": {**cfg["layers"][3]["mixer"], "q_rank": 5}}]}
+    shapes = lo.tensor_shapes(with_rank)
+    with pytest.raises(ValueError):
+        parse_layer_list(cfg, cls.family, None)              # the last layer's query latent size is in no config key
+    sc, layers = parse_layer_list(cfg, cls.family, shapes)
+    assert (sc.norm_kind, sc.post_norm, sc.no_pre_norm, sc.embed_norm, sc.streams) == (_seqabi.DN_NORM_RMS, 1, 1, 0, 0)
+    assert abs(sc.embed_scale - 0.25) < 1e-7 and abs(sc.eps - 1e-5) < 1e-9
+    assert all(l.mixer == _seqabi.DN_MIX_LATENT and l.kv_heads == 1 and l.kv_rank == 20 and l.rot_part == 6 and l.rot_dims == 6 for l in layers)
+    assert [l.q_rank for l in layers] == [0, 12, 0, 5] and [l.out_gate for l in layers] == [0, 1, 0, 1]
+    assert [l.rot_layout for l in layers] == [_seqabi.DN_ROT_INTERLEAVED, _seqabi.DN_ROT_HALF] * 2
+    assert [l.chunk for l in layers] == [9, 9, 0, 9] and all(l.mask_kind == _seqabi.DN_MASK_WINDOW for l in layers)
+    assert (layers[0].mlp_kind, layers[0].ff, layers[0].ff_act) == (_seqabi.DN_MLP_DENSE, 40, _seqabi.DN_FF_RELU2)
+    m1 = layers[1]
+    assert (m1.mlp_kind, m1.router_kind, m1.expert_act) == (_seqabi.DN_MLP_MOE, _seqabi.DN_ROUTER_SCORED, _seqabi.DN_EXPERT_SWIGLU)
+    assert (m1.experts, m1.identity, m1.top, m1.groups, m1.groups_keep, m1.ff, m1.shared_ff, m1.shared_gate) == (6, 2, 2, 4, 3, 24, 16, 1)
+    assert abs(m1.router_scale - 1.5) < 1e-7
+    m2 = layers[2]
+    assert (m2.experts, m2.identity, m2.top, m2.groups, m2.shared_ff, m2.shared_gate) == (4, 0, 1, 0, 0, 0) and abs(m2.router_scale - 1.0) < 1e-7
+    assert layers[3].ff == 0
+    m = cls.__new__(cls)
+    m.config, m._cfg_struct, m._layer_structs, m.hidden_size, m.vocab_size = cfg, sc, layers, sc.width, sc.vocab
+    want = m.expected_tensors()
+    assert "head" not in want                                # the embedding table is the head
+    got = {}
+    for key, sh in shapes.items():
+        if _LAYER_KEY.match(key):
+            lname, suffix = key.split(".", 1)
+            kind = cfg["layers"][int(lname[1:])]["type"]
+            suffix = cls.tensor_alias.get(kind, {}).get(suffix, cls.tensor_alias["*"].get(suffix, suffix))
+            key = f"{lname}.{suffix}"
+        got[key] = tuple(sh)
+    assert got == {k: tuple(v) for k, v in want.items()}
+    for k in want:
+        if _LAYER_KEY.match(k) and ".mlp.e" not in k:
+            assert k.split(".", 1)[1] in _seqabi.LAYER_SLOT, k
+
+
+def test_lutesun_oracle_by_hand():
+    """the oracle's pieces on numbers small enough to follow"""
+    from oracle import lutesun_oracle as lo
+
+    z = torch.log(torch.tensor([0.05, 0.30, 0.10, 0.25, 0.20, 0.10], dtype=torch.float64))
+    corr = torch.tensor([0.0, 0.0, 0.5, 0.0, 0.0, 0.0], dtype=torch.float64)
+    # groups (0,1) (2,3) (4,5): best corrected scores 0.30, 0.60, 0.20 -> keep the first two; choices 2 (0.60) and 1 (0.30)
+    ch, wt = lo.scored_router(z, corr, top=2, groups=3, keep=2, scale=2.0)
+    assert ch == [2, 1]
+    assert abs(wt[0] - 2.0 * 0.10 / 0.40) < 1e-12 and abs(wt[1] - 2.0 * 0.30 / 0.40) < 1e-12
+    ch, _ = lo.scored_router(z, None, top=3, groups=3, keep=1, scale=1.0)         # only group 0 is left: 1, 0, then nothing else
+    assert ch == [1, 0]
+    ch, _ = lo.scored_router(z, -corr * 10, top=2, groups=0, keep=0, scale=1.0)   # a negative choice score still beats a dropped one
+    assert ch == [1, 3]
+    # window: a query sees itself and size - 1 tokens before it
+    vis = lo.window_mask(6, 3)
+    assert vis[4].tolist() == [False, False, True, True, True, False] and vis[1].tolist() == [True, True, False, False, False, False]
+    assert lo.window_mask(4, 0).tolist() == torch.ones(4, 4).tril().bool().tolist() and lo.window_mask(3, 1).tolist() == torch.eye(3).bool().tolist()
+    # rotary: both layouts keep lengths, leave the tail alone, and make scores depend on the distance only; they pair differently
+    z = torch.randn(5, 2, 6, dtype=torch.float64)
+    for layout in ("interleaved", "half"):
+        r = lo.rotary(z, torch.arange(5), 4, 100.0, layout)
+        assert torch.equal(r[..., 4:], z[..., 4:]) and torch.allclose(r[0], z[0]) and torch.allclose(r.pow(2).sum(-1), z.pow(2).sum(-1))
+        q, k = torch.randn(1, 4, dtype=torch.float64), torch.randn(1, 4, dtype=torch.float64)
+        s = [float((lo.rotary(q, torch.tensor([a]), 4, 100.0, layout) * lo.rotary(k, torch.tensor([a - 3]), 4, 100.0, layout)).sum()) for a in (3, 50)]
+        assert abs(s[0] - s[1]) < 1e-9
+    e0 = torch.tensor([[1.0, 0.0, 0.0, 0.0]], dtype=torch.float64)
+    quarter = torch.tensor([1])      # frequency 1 on pair 0: position 1 turns it by one radian
+    a, b = lo.rotary(e0, quarter, 4, 100.0, "interleaved")[0], lo.rotary(e0, quarter, 4, 100.0, "half")[0]
+    assert abs(float(a[1]) - math.sin(1.0)) < 1e-12 and abs(float(b[2]) - math.sin(1.0)) < 1e-12 and float(a[2]) == 0.0 and float(b[1]) == 0.0
+    # norms: the one-plus weight is stored around zero
+    x = torch.tensor([[3.0, 4.0]], dtype=torch.float64)
+    assert torch.allclose(lo.rms_one_plus(x, torch.zeros(2, dtype=torch.float64), 0.0), lo.rms_plain(x, torch.ones(2, dtype=torch.float64), 0.0))
+    assert torch.allclose(lo.unit_rms(x, 0.0), x / math.sqrt(12.5))
 
 
 def test_filinex_oracle_recurrences_by_hand():
