@@ -41,7 +41,8 @@ MODEL_SLOT = {"embed": 100, "final.norm": 101, "head": 102, "final.norm.b": 103,
 EXPERT_SLOT = {"gate": 0, "up": 1, "down": 2}
 # phases of a step, in the header's order (dn_seq_profile_read)
 PHASES = ["embed", "norm", "proj", "attn_prep", "attn", "delta_prep", "delta_rule", "delta_out", "conv_carry", "out_proj",
-          "write_back", "ff_up", "ff_down", "head", "other", "recur_prep", "recur", "recur_out", "router", "moe_up", "moe_down"]
+          "write_back", "ff_up", "ff_down", "head", "other", "recur_prep", "recur", "recur_out", "router", "moe_up", "moe_down",
+          "latent_in", "latent_out"]
 
 
 class LayerCfg(C.Structure):

@@ -21,6 +21,9 @@
 //                in fp32 with one rounding                     -> Y[t][n]
 //   EPI_TANH   : y = T(tanh(acc))                              -> Y[t][n]
 //   EPI_CGLU   : two weight tiles; g = min(acc_g, limit), u = clamp(acc_u, -limit, limit), y = T(g sigmoid(1.702 g) (u + 1))
+//   EPI_SGLU   : two weight tiles; y = T(silu(acc_g) * acc_u), in fp32 with one rounding
+//   EPI_RELU2  : y = T(relu(acc + bias)^2)
+//   (EPI_STORE_F32 adds the bias too when there is one)
 //
 // GROUPED: one launch over many weight matrices of one shape (routed experts).  The token rows are sorted by matrix
 // into tiles of BN rows that never span two matrices; a device table gives every token tile its matrix, first row
@@ -32,8 +35,8 @@
 
 namespace dn {
 
-enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU = 2, EPI_STORE_F32 = 3, EPI_GEGLU = 4, EPI_CGLU = 5, EPI_TANH = 6 };
-__host__ __device__ constexpr bool epi_two_weights(int epi) { return epi == EPI_SWIGLU || epi == EPI_GEGLU || epi == EPI_CGLU; }
+enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU = 2, EPI_STORE_F32 = 3, EPI_GEGLU = 4, EPI_CGLU = 5, EPI_TANH = 6, EPI_SGLU = 7, EPI_RELU2 = 8 };
+__host__ __device__ constexpr bool epi_two_weights(int epi) { return epi == EPI_SWIGLU || epi == EPI_GEGLU || epi == EPI_CGLU || epi == EPI_SGLU; }
 
 constexpr int TC_BM = 128;        // weight rows per tile (MMA M)
 constexpr int TC_BK = 64;         // k-step: 64 bf16 = 128 bytes = one swizzle span
@@ -209,7 +212,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap mapW, const __grid_constant__ CUte
       tc_fence_after();
       const uint32_t trow = tmem_base + ab * ACC_COLS + ((uint32_t)(ew * 32) << 16);
       float bias = 0.f;
-      if (EPI == EPI_STORE && p.bias != nullptr && n < p.N) bias = __bfloat162float(p.bias[n]);
+      if ((EPI == EPI_STORE || EPI == EPI_STORE_F32 || EPI == EPI_RELU2) && p.bias != nullptr && n < p.N) bias = __bfloat162float(p.bias[n]);
       const int t_base = GROUPED ? p.g_tile_r0[tt] : tt * BN;
       const int t_end = GROUPED ? t_base + p.g_tile_rows[tt] : p.T;
 #pragma unroll 1
@@ -223,7 +226,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap mapW, const __grid_constant__ CUte
             const int t = t_base + c + j;
             if (t < t_end) {
               if (EPI == EPI_STORE_F32) {
-                reinterpret_cast<float*>(p.Y)[(size_t)t * p.ldy + p.col0 + n] = v[j];
+                reinterpret_cast<float*>(p.Y)[(size_t)t * p.ldy + p.col0 + n] = v[j] + bias;
                 continue;
               }
               float y;
@@ -232,6 +235,11 @@ k_gemm_tc(const __grid_constant__ CUtensorMap mapW, const __grid_constant__ CUte
                 y = 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * v2[j];
               } else if (EPI == EPI_TANH) {
                 y = tanhf(v[j]);
+              } else if (EPI == EPI_SGLU) {
+                y = v[j] / (1.0f + expf(-v[j])) * v2[j];
+              } else if (EPI == EPI_RELU2) {
+                const float r = fmaxf(v[j] + bias, 0.f);
+                y = r * r;
               } else if (EPI == EPI_CGLU) {
                 const float g = fminf(v[j], p.limit), u = fminf(fmaxf(v2[j], -p.limit), p.limit);
                 y = g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);

@@ -620,12 +620,14 @@ template <class T>
 static cudaError_t linear(dn_seq_model* m, cudaStream_t s, const T* X, const void* W, const void* W2, void* Y, int N, int O, int K, bool out32,
                           int act, LinMaps tm = LinMaps{nullptr, nullptr, nullptr}, float alim = 0.f, const void* bias = nullptr) {
   // (a weight of fewer than 128 rows fills part of a tile: still far ahead of the CUDA-core tiles once K is in the thousands)
-  if (std::is_same<T, bf16>::value && N >= 16 && O >= 16 && tm.w && tm.x && tm.x->ok && !bias &&
-      (act == ACT_NONE || act == ACT_TANH || ((act == ACT_GEGLU || act == ACT_CGLU) && tm.w2))) {
+  if (std::is_same<T, bf16>::value && N >= 16 && O >= 16 && tm.w && tm.x && tm.x->ok && (!bias || act == ACT_RELU2 || (act == ACT_NONE && out32)) &&
+      (act == ACT_NONE || act == ACT_TANH || act == ACT_RELU2 || (act_two(act) && tm.w2))) {
     dn::TcParams p;
     memset(&p, 0, sizeof(p));
-    p.T = N; p.N = O; p.K = K; p.ldy = O; p.Y = (dn::bf16*)Y; p.err = m->tc_err; p.limit = alim;
+    p.T = N; p.N = O; p.K = K; p.ldy = O; p.Y = (dn::bf16*)Y; p.err = m->tc_err; p.limit = alim; p.bias = (const dn::bf16*)bias;
     if (act == ACT_CGLU) return gemm_tc<dn::EPI_CGLU>(*tm.w, *tm.w2, *tm.x, p, s);
+    if (act == ACT_SWIGLU) return gemm_tc<dn::EPI_SGLU>(*tm.w, *tm.w2, *tm.x, p, s);
+    if (act == ACT_RELU2) return gemm_tc<dn::EPI_RELU2>(*tm.w, *tm.w, *tm.x, p, s);
     if (act == ACT_TANH) return gemm_tc<dn::EPI_TANH>(*tm.w, *tm.w, *tm.x, p, s);
     if (act) return gemm_tc<dn::EPI_GEGLU>(*tm.w, *tm.w2, *tm.x, p, s);
     if (out32) return gemm_tc<dn::EPI_STORE_F32>(*tm.w, *tm.w, *tm.x, p, s);
@@ -669,6 +671,31 @@ static cudaError_t attn_tiles(cudaStream_t s, const Batch& b, const bf16* q, con
   AT(2, 0, 128, 32) AT(2, 1, 128, 64) AT(2, 2, 128, 128)
 #undef AT
   return cudaErrorInvalidValue;
+}
+
+// latent attention of a step that brings a prompt portion, bf16: the MMA tiles over the cached rows (R + rot numbers a key,
+// the first R the value) when the rows start on 16-byte boundaries
+static bool latent_tiles_ok(const Batch& b, int Ck, int R) { return b.max_len >= 16 && Ck % 8 == 0 && R % 2 == 0 && R <= 512; }
+template <int DVH>
+static cudaError_t latent_tiles_launch(cudaStream_t s, const Batch& b, const bf16* q, const bf16* pool, int H, int Ck, int R, int chunk, float scale,
+                                       const AttnExtra& ex, bf16* out) {
+  const int DKP = (Ck + 15) / 16 * 16, LD = std::max(DKP, 2 * DVH) + 8;
+  const size_t smem = (size_t)2 * 64 * LD * 2;
+  static size_t attr = 0;
+  if (smem > attr) {
+    cudaError_t e = cudaFuncSetAttribute(k_latent_tiles<DVH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    attr = smem;
+  }
+  g_launches++;
+  k_latent_tiles<DVH><<<dim3(b.row_tiles, H), 256, smem, s>>>(b, q, pool, H, Ck, R, DKP, LD, chunk, scale, ex, out);
+  return cudaGetLastError();
+}
+static cudaError_t latent_tiles(cudaStream_t s, const Batch& b, const bf16* q, const bf16* pool, int H, int Ck, int R, int chunk, float scale,
+                                const AttnExtra& ex, bf16* out) {
+  if (R <= 128) return latent_tiles_launch<64>(s, b, q, pool, H, Ck, R, chunk, scale, ex, out);
+  if (R <= 256) return latent_tiles_launch<128>(s, b, q, pool, H, Ck, R, chunk, scale, ex, out);
+  return latent_tiles_launch<256>(s, b, q, pool, H, Ck, R, chunk, scale, ex, out);
 }
 
 // phase boundary: the time from this mark to the next one is booked on `phase`
@@ -728,7 +755,7 @@ static int moe_ff(dn_seq_model* m, SeqLayer& l, int N, bool fused, NextNorm<T> n
   } else {
     MoePlan pl{m->rpos, m->rtok, m->tiles, m->tiles + m->max_tiles, m->tiles + 2 * m->max_tiles, m->tiles + 3 * m->max_tiles};
     const int mt = std::min(m->max_tiles, P / MOE_ROWS + E + 1);
-    bool tc = std::is_same<T, bf16>::value && m->x_xg_ok && l.x_eact_ok && l.emaps_d && lc.ff >= 32 && W >= 32 && eact == ACT_CGLU;
+    bool tc = std::is_same<T, bf16>::value && m->x_xg_ok && l.x_eact_ok && l.emaps_d && lc.ff >= 32 && W >= 32;
     for (char ok : l.emap_ok) tc = tc && ok;
     // rows of a token tile: 128 (the tensor cores read the weight tile once for twice the tokens) when an expert gets
     // two such tiles on average, else 64 (less padding); the CUDA-core tiles are 64 rows
@@ -742,7 +769,10 @@ static int moe_ff(dn_seq_model* m, SeqLayer& l, int N, bool fused, NextNorm<T> n
       p.g_tile_e = pl.tile_e; p.g_tile_r0 = pl.tile_r0; p.g_tile_rows = pl.tile_rows; p.g_ntiles = pl.n_tiles;
       CK(mark(m, DN_SEQ_PH_MOE_UP, s));
       p.T = P; p.N = lc.ff; p.K = W; p.ldy = lc.ff; p.Y = (dn::bf16*)m->eact; p.g_mapW = l.emaps_d; p.g_mapW2 = l.emaps_d + E;
-      if (tile_rows == 128) CK(gemm_tc_grouped<dn::EPI_CGLU, 128>(m->x_xg[1], p, s));
+      if (eact == ACT_SWIGLU) {
+        if (tile_rows == 128) CK(gemm_tc_grouped<dn::EPI_SGLU, 128>(m->x_xg[1], p, s));
+        else CK(gemm_tc_grouped<dn::EPI_SGLU, 64>(m->x_xg[0], p, s));
+      } else if (tile_rows == 128) CK(gemm_tc_grouped<dn::EPI_CGLU, 128>(m->x_xg[1], p, s));
       else CK(gemm_tc_grouped<dn::EPI_CGLU, 64>(m->x_xg[0], p, s));
       CK(mark(m, DN_SEQ_PH_MOE_DOWN, s));
       p.N = W; p.K = lc.ff; p.ldy = W; p.Y = (dn::bf16*)m->eo; p.g_mapW = l.emaps_d + 2 * E; p.g_mapW2 = l.emaps_d + 2 * E;
@@ -932,17 +962,23 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
         CK(launch(k_rms_rows<T>, dim3(N), dim3(128), 0, s, (T*)m->lr, lc.q_rank, w(DN_SQ_DQ_NORM), c.eps));
         CK(linear<T>(m, s, (const T*)m->lr, l.w[DN_SQ_Q], nullptr, m->uq, N, l.Cq, lc.q_rank, false, 0, LinMaps{wm(DN_SQ_Q), nullptr, &l.x_lr}));
       }
-      PH(DN_SEQ_PH_ATTN_PREP);
+      PH(DN_SEQ_PH_LATENT_IN);
       LatentPrep a{lc.heads, lc.dim, dr, R, lc.rot_dims, lc.rot_layout == DN_ROT_HALF ? 1 : 0, c.eps, l.inv_freq};
       T* pool = (T*)m->kpool[run.kv_index];
       CK(launch(k_latent_prep<T>, dim3(N), dim3(256), 0, s, a, b, (const T*)m->uq, (const T*)m->uk, w(DN_SQ_DKV_NORM), (T*)m->qb, pool));
       // the unrotated query parts into the latent space: qb[n, h, 0:R] = W_uk,h^T q[n, h, 0:dim]
-      CK(launch(k_linear_heads<T>, dim3((R + 63) / 64, (N + 63) / 64, lc.heads), dim3(256), 0, s, (const T*)m->uq, w(DN_SQ_UK), (T*)m->qb, N, R, lc.dim,
-                HeadsGeom{l.Cq, dq, l.Cql, l.Ck, (size_t)lc.dim * R, 1, R}));
+      if (few && (size_t)N * lc.dim * 4 <= 48 * 1024)
+        CK(launch(k_absorb_few<T>, dim3((R + 127) / 128, lc.heads), dim3(128), (size_t)N * lc.dim * 4, s, (const T*)m->uq, w(DN_SQ_UK), (T*)m->qb, N, lc.heads,
+                  lc.dim, dq, R, l.Ck));
+      else
+        CK(launch(k_linear_heads<T>, dim3((R + 63) / 64, (N + 63) / 64, lc.heads), dim3(256), 0, s, (const T*)m->uq, w(DN_SQ_UK), (T*)m->qb, N, R, lc.dim,
+                  HeadsGeom{l.Cq, dq, l.Cql, l.Ck, (size_t)lc.dim * R, 1, R}));
       // multi-query attention of all heads over the cached rows: keys [R + dr], values = their first R numbers
       PH(DN_SEQ_PH_ATTN);
       AttnExtra ex{lc.softcap, nullptr, lc.out_gate ? (const float*)m->pa : nullptr, lc.mask_kind == DN_MASK_WINDOW ? 1 : 0, l.Ck};
-      {
+      if (std::is_same<T, bf16>::value && latent_tiles_ok(b, l.Ck, R))
+        CK(latent_tiles(s, b, (const bf16*)m->qb, (const bf16*)pool, lc.heads, l.Ck, R, lc.chunk, lc.scale, ex, (bf16*)m->gt));
+      else {
         const int Z = N <= AT_SPLIT_ROWS ? AT_MAX_SPLITS : 1;
         const size_t sm = (size_t)(((l.Ck + 3) & ~3) + AT_WARPS * (2 + (R + 31) / 32 * 32)) * 4;
         if (R <= 256)
@@ -954,8 +990,12 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
         if (Z > 1) CK(launch(k_attn_merge<T>, dim3(N, lc.heads), dim3(128), 0, s, b, lc.heads, R, lc.chunk, Z, ex, (const float*)m->attn_part, (T*)m->gt));
       }
       // out of the latent space: mo[n, h, :] = W_uv,h gt[n, h, :]
-      CK(launch(k_linear_heads<T>, dim3((lc.vdim + 63) / 64, (N + 63) / 64, lc.heads), dim3(256), 0, s, (const T*)m->gt, w(DN_SQ_UV), (T*)m->mo, N, lc.vdim, R,
-                HeadsGeom{l.Col, R, l.Co, lc.vdim, (size_t)lc.vdim * R, R, 1}));
+      PH(DN_SEQ_PH_LATENT_OUT);
+      if (few)
+        CK(launch(k_upv_few<T>, dim3((l.Co + 7) / 8), dim3(256), 0, s, (const T*)m->gt, w(DN_SQ_UV), (T*)m->mo, N, lc.heads, lc.vdim, R));
+      else
+        CK(launch(k_linear_heads<T>, dim3((lc.vdim + 63) / 64, (N + 63) / 64, lc.heads), dim3(256), 0, s, (const T*)m->gt, w(DN_SQ_UV), (T*)m->mo, N, lc.vdim, R,
+                  HeadsGeom{l.Col, R, l.Co, lc.vdim, (size_t)lc.vdim * R, R, 1}));
     } else if (lc.mixer == DN_MIX_DELTA) {
       if (!few) {
         CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_A], nullptr, m->pa, N, lc.heads, W, true, 0, LinMaps{wm(DN_SQ_A), nullptr, &m->x_h}));

@@ -16,6 +16,7 @@
 // Rotary pairs are (2i, 2i + 1) or (i, i + rot / 2), on the first `rot` numbers of the rotated part; angles are fp32.
 #pragma once
 #include "dn_seq_kernels.cuh"
+#include "dn_seq_moe.cuh"      // warp_dot
 
 namespace dnseq {
 
@@ -147,6 +148,194 @@ __global__ void __launch_bounds__(256) k_linear_heads(const T* __restrict__ X, c
     for (int j = 0; j < 4; j++) {
       const int o = o0 + tx * 4 + j;
       if (o < O) stf(Yz + (size_t)n * g.ldy + o, acc[i][j]);
+    }
+  }
+}
+
+
+// The same two products for a few tokens (N <= 8: decode steps), each weight read once.
+// Into the latent space: thread r of block (r-chunk, head) walks the rows of W_uk,h -- adjacent threads read adjacent
+// numbers -- against the tokens' unrotated query parts held in shared memory; sums in ascending d.
+template <class T>
+__global__ void __launch_bounds__(128) k_absorb_few(const T* __restrict__ Uq, const T* __restrict__ Wuk, T* __restrict__ qout, int N, int H, int dn,
+                                                    int dq, int R, int Ck) {
+  extern __shared__ float qs[];      // [N][dn]
+  const int h = blockIdx.y, r = blockIdx.x * blockDim.x + threadIdx.x;
+  for (int i = threadIdx.x; i < N * dn; i += blockDim.x) qs[i] = ldf(Uq + ((size_t)(i / dn) * H + h) * dq + i % dn);
+  __syncthreads();
+  if (r >= R) return;
+  float acc[8];
+#pragma unroll
+  for (int n = 0; n < 8; n++) acc[n] = 0.f;
+  const T* w = Wuk + (size_t)h * dn * R + r;
+#pragma unroll 4
+  for (int d = 0; d < dn; d++) {
+    const float wv = ldf(w + (size_t)d * R);
+#pragma unroll
+    for (int n = 0; n < 8; n++)
+      if (n < N) acc[n] = fmaf(qs[n * dn + d], wv, acc[n]);
+  }
+#pragma unroll
+  for (int n = 0; n < 8; n++)
+    if (n < N) stf(qout + ((size_t)n * H + h) * Ck + r, acc[n]);
+}
+// Out of the latent space: one warp per output feature (head h, value dim j) streams its row of W_uv
+template <class T>
+__global__ void __launch_bounds__(256) k_upv_few(const T* __restrict__ X, const T* __restrict__ Wuv, T* __restrict__ Y, int N, int H, int dv, int R) {
+  const int o = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (o >= H * dv) return;
+  const int h = o / dv;
+  const T* w = Wuv + (size_t)o * R;
+  const bool vec = R % Vec16<T>::n == 0 && ((((uintptr_t)X | (uintptr_t)Wuv) & 15) == 0);
+  for (int n = 0; n < N; n++) {
+    const float a = warp_dot(X + ((size_t)n * H + h) * R, w, R, vec);
+    if (lane == 0) stf(Y + (size_t)n * H * dv + o, a);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Latent attention of prompt portions, bf16, on the warp-level tensor-core MMA (m16n8k16, fp32 accumulation).
+// A block owns 64 consecutive query rows of one entry and one head.  A key tile is one page of cached rows, staged
+// once through shared memory and used twice: all R + rot numbers of a row as the key, its first R numbers as the value
+// (ldmatrix.trans on the same tile), so a page is read once per (row tile, head).  Eight warps: warp w takes the 16 rows
+// (w & 3) and the half (w >> 2) of the value columns -- with a latent of 512 the output accumulators of 16 rows x 256
+// columns are 128 registers a thread; both halves compute the same scores.  The query tile stays in shared memory
+// (its fragments are re-read per key tile: 576 numbers a row do not fit the registers beside the accumulators).
+// Scores, running maximum and sum are fp32; the weights enter P V as a bf16 pair (hi + lo).  Per row the key tiles are
+// visited in ascending position and a tile the row does not see changes nothing: the result does not depend on the cut.
+// DVH: value columns a warp owns (the block covers 2 DVH >= R).  LD: shared row pitch = max(padded key size, 2 DVH) + 8.
+__device__ __forceinline__ void load_tile_rt(bf16* __restrict__ dst, const bf16* __restrict__ src, size_t ld, int cols, int valid, int LD) {
+  const int vec = LD / 8 - 1;      // 16-byte groups per row, the pad group left out
+  for (int e = threadIdx.x; e < 64 * vec; e += blockDim.x) {
+    const int r = e / vec, c = (e % vec) * 8;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < valid && c < cols) v = *reinterpret_cast<const uint4*>(src + (size_t)r * ld + c);
+    *reinterpret_cast<uint4*>(dst + (size_t)r * LD + c) = v;
+  }
+}
+template <int DVH>
+__global__ void __launch_bounds__(256, 1) k_latent_tiles(Batch b, const bf16* __restrict__ q, const bf16* __restrict__ kpool, int H, int Ck, int R,
+                                                         int DKP, int LD, int chunk, float scale, AttnExtra ex, bf16* __restrict__ out) {
+  extern __shared__ __align__(16) unsigned char smraw[];
+  bf16* Qs = reinterpret_cast<bf16*>(smraw);
+  bf16* Ks = Qs + 64 * LD;
+  int e = 0, t = blockIdx.x;
+  for (; e < b.E; e++) {
+    const int nt = (b.ent_start[e + 1] - b.ent_start[e] + 63) / 64;
+    if (t < nt) break;
+    t -= nt;
+  }
+  if (e >= b.E) return;
+  const int h = blockIdx.y;
+  const int s0 = b.ent_start[e] + t * 64, s1 = b.ent_start[e + 1];
+  const int rows = min(64, s1 - s0);
+  const int p_first = b.ent_pos0[e] + t * 64, p_last = p_first + rows - 1;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, rg = warp & 3, hv = warp >> 2;
+  load_tile_rt(Qs, q + ((size_t)s0 * H + h) * Ck, (size_t)H * Ck, Ck, rows, LD);
+  const int r0 = rg * 16 + (lane >> 2), r1 = r0 + 8;
+  const int p0 = r0 < rows ? p_first + r0 : -1, p1 = r1 < rows ? p_first + r1 : -1;
+  const int lo0 = p0 >= 0 ? attn_lo(p0, chunk, ex.window) : 0, lo1 = p1 >= 0 ? attn_lo(p1, chunk, ex.window) : 0;
+  const bool warp_live = rg * 16 < rows;
+  float o[DVH / 8][4];
+#pragma unroll
+  for (int j = 0; j < DVH / 8; j++) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  const int32_t* bt = b.bt + (size_t)b.ent_slot[e] * b.max_pages;
+  const int lo_tile = attn_lo(p_first, chunk, ex.window);
+  const bf16* qrow = Qs + (size_t)(rg * 16 + (lane & 15)) * LD + (lane >> 4) * 8;
+  for (int j0 = (lo_tile / PAGE) * PAGE; j0 <= p_last; j0 += PAGE) {
+    const size_t prow = (size_t)bt[j0 / PAGE] * PAGE;
+    const int kvalid = min(PAGE, p_last - j0 + 1);
+    __syncthreads();
+    load_tile_rt(Ks, kpool + prow * Ck, (size_t)Ck, Ck, kvalid, LD);
+    __syncthreads();
+    if (!warp_live) continue;
+    float sc[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; j++) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+#pragma unroll 2
+    for (int kk = 0; kk < DKP / 16; kk++) {
+      uint32_t qf[4];
+      ldsm_x4(qf, qrow + kk * 16);
+#pragma unroll
+      for (int jj = 0; jj < 4; jj++) {
+        uint32_t kf[4];
+        ldsm_x4(kf, Ks + (size_t)(jj * 16 + (lane >> 4) * 8 + (lane & 7)) * LD + kk * 16 + ((lane >> 3) & 1) * 8);
+        mma_bf16(sc[2 * jj], qf, kf[0], kf[1]);
+        mma_bf16(sc[2 * jj + 1], qf, kf[2], kf[3]);
+      }
+    }
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+#pragma unroll
+      for (int i = 0; i < 2; i++) {
+        const int key = j0 + j * 8 + (lane & 3) * 2 + i;
+        float a0 = sc[j][i] * scale, a1 = sc[j][2 + i] * scale;
+        if (ex.softcap > 0.f) { a0 = ex.softcap * tanhf(a0 / ex.softcap); a1 = ex.softcap * tanhf(a1 / ex.softcap); }
+        sc[j][i] = (key <= p0 && key >= lo0) ? a0 : -INFINITY;
+        sc[j][2 + i] = (key <= p1 && key >= lo1) ? a1 : -INFINITY;
+        mx0 = fmaxf(mx0, sc[j][i]);
+        mx1 = fmaxf(mx1, sc[j][2 + i]);
+      }
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+    const float u0 = n0 == -INFINITY ? 0.f : n0, u1 = n1 == -INFINITY ? 0.f : n1;      // nothing seen yet: weights are 0
+    const float c0 = expf(m0 - u0), c1 = expf(m1 - u1);
+    float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+#pragma unroll
+      for (int i = 0; i < 2; i++) {
+        sc[j][i] = expf(sc[j][i] - u0);
+        sc[j][2 + i] = expf(sc[j][2 + i] - u1);
+        ps0 += sc[j][i];
+        ps1 += sc[j][2 + i];
+      }
+    }
+    ps0 += __shfl_xor_sync(0xffffffffu, ps0, 1); ps0 += __shfl_xor_sync(0xffffffffu, ps0, 2);
+    ps1 += __shfl_xor_sync(0xffffffffu, ps1, 1); ps1 += __shfl_xor_sync(0xffffffffu, ps1, 2);
+    l0 = l0 * c0 + ps0; l1 = l1 * c1 + ps1;
+    m0 = n0; m1 = n1;
+#pragma unroll
+    for (int j = 0; j < DVH / 8; j++) { o[j][0] *= c0; o[j][1] *= c0; o[j][2] *= c1; o[j][3] *= c1; }
+    // O += P V with P = hi + lo; V = the first columns of the key tile
+#pragma unroll
+    for (int kk = 0; kk < 4; kk++) {
+      uint32_t ph[4], pl[4];
+#pragma unroll
+      for (int x = 0; x < 4; x++) {
+        const float a = sc[2 * kk + (x >> 1)][(x & 1) * 2], c = sc[2 * kk + (x >> 1)][(x & 1) * 2 + 1];
+        const float ah = __bfloat162float(__float2bfloat16_rn(a)), ch = __bfloat162float(__float2bfloat16_rn(c));
+        ph[x] = pack_bf16(ah, ch);
+        pl[x] = pack_bf16(a - ah, c - ch);
+      }
+      const bf16* vrow = Ks + (size_t)(kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * LD + hv * DVH + (lane >> 4) * 8;
+#pragma unroll
+      for (int jj = 0; jj < DVH / 16; jj++) {
+        uint32_t vf[4];
+        ldsm_x4_t(vf, vrow + jj * 16);
+        mma_bf16(o[2 * jj], ph, vf[0], vf[1]);
+        mma_bf16(o[2 * jj + 1], ph, vf[2], vf[3]);
+        mma_bf16(o[2 * jj], pl, vf[0], vf[1]);
+        mma_bf16(o[2 * jj + 1], pl, vf[2], vf[3]);
+      }
+    }
+  }
+  if (!warp_live) return;
+  float i0 = p0 >= 0 ? 1.f / l0 : 0.f, i1 = p1 >= 0 ? 1.f / l1 : 0.f;
+  if (ex.gate) {
+    if (p0 >= 0) i0 *= sigmoid_f(ex.gate[(size_t)(s0 + r0) * H + h]);
+    if (p1 >= 0) i1 *= sigmoid_f(ex.gate[(size_t)(s0 + r1) * H + h]);
+  }
+#pragma unroll
+  for (int j = 0; j < DVH / 8; j++) {
+    const int d = hv * DVH + j * 8 + (lane & 3) * 2;
+    if (d < R) {
+      if (p0 >= 0) *reinterpret_cast<uint32_t*>(out + ((size_t)(s0 + r0) * H + h) * R + d) = pack_bf16(o[j][0] * i0, o[j][1] * i0);
+      if (p1 >= 0) *reinterpret_cast<uint32_t*>(out + ((size_t)(s0 + r1) * H + h) * R + d) = pack_bf16(o[j][2] * i1, o[j][3] * i1);
     }
   }
 }

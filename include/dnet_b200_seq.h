@@ -187,7 +187,10 @@ enum {
   DN_SEQ_PH_EMBED = 0, DN_SEQ_PH_NORM, DN_SEQ_PH_PROJ, DN_SEQ_PH_ATTN_PREP, DN_SEQ_PH_ATTN, DN_SEQ_PH_DELTA_PREP,
   DN_SEQ_PH_DELTA_RULE, DN_SEQ_PH_DELTA_OUT, DN_SEQ_PH_CARRY, DN_SEQ_PH_OUT_PROJ, DN_SEQ_PH_WRITE_BACK, DN_SEQ_PH_FF_UP,
   DN_SEQ_PH_FF_DOWN, DN_SEQ_PH_HEAD, DN_SEQ_PH_OTHER, DN_SEQ_PH_RECUR_PREP, DN_SEQ_PH_RECUR, DN_SEQ_PH_RECUR_OUT, DN_SEQ_PH_ROUTER,
-  DN_SEQ_PH_MOE_UP, DN_SEQ_PH_MOE_DOWN, DN_SEQ_PH_COUNT
+  DN_SEQ_PH_MOE_UP, DN_SEQ_PH_MOE_DOWN,
+  DN_SEQ_PH_LATENT_IN,    /* latent attention: the cached row, rotary, queries absorbed into the latent space */
+  DN_SEQ_PH_LATENT_OUT,   /* latent attention: the heads' outputs taken out of the latent space */
+  DN_SEQ_PH_COUNT
 };
 int dn_seq_profile(dn_seq_model* m, int on);
 int dn_seq_profile_read(dn_seq_model* m, double* ms_out, int reset);
