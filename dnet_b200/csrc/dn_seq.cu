@@ -967,9 +967,14 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
       T* pool = (T*)m->kpool[run.kv_index];
       CK(launch(k_latent_prep<T>, dim3(N), dim3(256), 0, s, a, b, (const T*)m->uq, (const T*)m->uk, w(DN_SQ_DKV_NORM), (T*)m->qb, pool));
       // the unrotated query parts into the latent space: qb[n, h, 0:R] = W_uk,h^T q[n, h, 0:dim]
-      if (few && (size_t)N * lc.dim * 4 <= 48 * 1024)
-        CK(launch(k_absorb_few<T>, dim3((R + 127) / 128, lc.heads), dim3(128), (size_t)N * lc.dim * 4, s, (const T*)m->uq, w(DN_SQ_UK), (T*)m->qb, N, lc.heads,
+      // (all strides multiples of 8 numbers: 16-byte operand rows for the MMA form)
+      const bool heads_mma = std::is_same<T, bf16>::value && N >= 16 && dq % 8 == 0 && lc.dim % 8 == 0 && R % 8 == 0 && dr % 8 == 0 && lc.vdim % 8 == 0;
+      if (few && (size_t)N * lc.dim * 4 <= 40 * 1024)
+        CK(launch(k_absorb_few<T>, dim3((R + 31) / 32, lc.heads), dim3(128), (size_t)(N * lc.dim + 4 * 8 * 32) * 4, s, (const T*)m->uq, w(DN_SQ_UK), (T*)m->qb, N, lc.heads,
                   lc.dim, dq, R, l.Ck));
+      else if (heads_mma)
+        CK(launch(k_heads_mma<true>, dim3((R + 127) / 128, (N + 63) / 64, lc.heads), dim3(128), 0, s, (const bf16*)m->uq, (const bf16*)l.w[DN_SQ_UK], (bf16*)m->qb, N, R,
+                  lc.dim, HeadsGeom{l.Cq, dq, l.Cql, l.Ck, (size_t)lc.dim * R, 1, R}));
       else
         CK(launch(k_linear_heads<T>, dim3((R + 63) / 64, (N + 63) / 64, lc.heads), dim3(256), 0, s, (const T*)m->uq, w(DN_SQ_UK), (T*)m->qb, N, R, lc.dim,
                   HeadsGeom{l.Cq, dq, l.Cql, l.Ck, (size_t)lc.dim * R, 1, R}));
@@ -993,6 +998,9 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
       PH(DN_SEQ_PH_LATENT_OUT);
       if (few)
         CK(launch(k_upv_few<T>, dim3((l.Co + 7) / 8), dim3(256), 0, s, (const T*)m->gt, w(DN_SQ_UV), (T*)m->mo, N, lc.heads, lc.vdim, R));
+      else if (heads_mma)
+        CK(launch(k_heads_mma<false>, dim3((lc.vdim + 127) / 128, (N + 63) / 64, lc.heads), dim3(128), 0, s, (const bf16*)m->gt, (const bf16*)l.w[DN_SQ_UV], (bf16*)m->mo, N,
+                  lc.vdim, R, HeadsGeom{l.Col, R, l.Co, lc.vdim, (size_t)lc.vdim * R, R, 1}));
       else
         CK(launch(k_linear_heads<T>, dim3((lc.vdim + 63) / 64, (N + 63) / 64, lc.heads), dim3(256), 0, s, (const T*)m->gt, w(DN_SQ_UV), (T*)m->mo, N, lc.vdim, R,
                   HeadsGeom{l.Col, R, l.Co, lc.vdim, (size_t)lc.vdim * R, R, 1}));

@@ -714,7 +714,8 @@ __global__ void __launch_bounds__(AT_WARPS * 32) k_attn(Batch b, const T* __rest
       const T* kr = kpool + ((size_t)bt[j / PAGE] * PAGE + (j % PAGE)) * Ck + g * dk;
       float d0 = 0.f;
       if (kvec) {
-        for (int d = 0; d < dk; d += V) {
+#pragma unroll 8
+        for (int d = 0; d < dk; d += V) {      // (unrolled: the loads of a long key row are issued ahead of the sums)
           uint4 raw = *reinterpret_cast<const uint4*>(kr + d);
           const T* e = reinterpret_cast<const T*>(&raw);
 #pragma unroll

@@ -154,30 +154,39 @@ __global__ void __launch_bounds__(256) k_linear_heads(const T* __restrict__ X, c
 
 
 // The same two products for a few tokens (N <= 8: decode steps), each weight read once.
-// Into the latent space: thread r of block (r-chunk, head) walks the rows of W_uk,h -- adjacent threads read adjacent
-// numbers -- against the tokens' unrotated query parts held in shared memory; sums in ascending d.
+// Into the latent space: a block owns 32 latent numbers of one head; its four warps split the rows of W_uk,h (lane r reads
+// column r of a row: adjacent lanes, adjacent numbers) against the tokens' unrotated query parts in shared memory, and
+// the warps' partial sums are added in warp order.
 template <class T>
 __global__ void __launch_bounds__(128) k_absorb_few(const T* __restrict__ Uq, const T* __restrict__ Wuk, T* __restrict__ qout, int N, int H, int dn,
                                                     int dq, int R, int Ck) {
-  extern __shared__ float qs[];      // [N][dn]
-  const int h = blockIdx.y, r = blockIdx.x * blockDim.x + threadIdx.x;
+  extern __shared__ float qs[];      // [N][dn], then [4][8][32] partial sums
+  float* part = qs + N * dn;
+  const int h = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, r = blockIdx.x * 32 + lane;
   for (int i = threadIdx.x; i < N * dn; i += blockDim.x) qs[i] = ldf(Uq + ((size_t)(i / dn) * H + h) * dq + i % dn);
   __syncthreads();
-  if (r >= R) return;
   float acc[8];
 #pragma unroll
   for (int n = 0; n < 8; n++) acc[n] = 0.f;
-  const T* w = Wuk + (size_t)h * dn * R + r;
-#pragma unroll 4
-  for (int d = 0; d < dn; d++) {
-    const float wv = ldf(w + (size_t)d * R);
+  const int per = (dn + 3) / 4, d0 = warp * per, d1 = min(dn, d0 + per);
+  if (r < R) {
+    const T* w = Wuk + (size_t)h * dn * R + r;
+#pragma unroll 8
+    for (int d = d0; d < d1; d++) {
+      const float wv = ldf(w + (size_t)d * R);
 #pragma unroll
-    for (int n = 0; n < 8; n++)
-      if (n < N) acc[n] = fmaf(qs[n * dn + d], wv, acc[n]);
+      for (int n = 0; n < 8; n++)
+        if (n < N) acc[n] = fmaf(qs[n * dn + d], wv, acc[n]);
+    }
   }
 #pragma unroll
-  for (int n = 0; n < 8; n++)
-    if (n < N) stf(qout + ((size_t)n * H + h) * Ck + r, acc[n]);
+  for (int n = 0; n < 8; n++) part[(warp * 8 + n) * 32 + lane] = acc[n];
+  __syncthreads();
+  if (warp == 0 && r < R) {
+#pragma unroll
+    for (int n = 0; n < 8; n++)
+      if (n < N) stf(qout + ((size_t)n * H + h) * Ck + r, ((part[n * 32 + lane] + part[(8 + n) * 32 + lane]) + part[(16 + n) * 32 + lane]) + part[(24 + n) * 32 + lane]);
+  }
 }
 // Out of the latent space: one warp per output feature (head h, value dim j) streams its row of W_uv
 template <class T>
@@ -336,6 +345,73 @@ __global__ void __launch_bounds__(256, 1) k_latent_tiles(Batch b, const bf16* __
     if (d < R) {
       if (p0 >= 0) *reinterpret_cast<uint32_t*>(out + ((size_t)(s0 + r0) * H + h) * R + d) = pack_bf16(o[j][0] * i0, o[j][1] * i0);
       if (p1 >= 0) *reinterpret_cast<uint32_t*>(out + ((size_t)(s0 + r1) * H + h) * R + d) = pack_bf16(o[j][2] * i1, o[j][3] * i1);
+    }
+  }
+}
+
+// The two per-head products of a prompt portion, bf16, on the warp-level MMA (m16n8k16, fp32 accumulation): the geometry of
+// k_linear_heads, a block = 64 tokens x 128 output features of one head, four warps of 16 rows each, operands staged
+// through shared memory in k-chunks of 64.  WT: the weight lies [k][o] (o contiguous: the key up-projection read
+// transposed, ldmatrix.trans), else [o][k].  Needs 16-byte aligned rows: every stride a multiple of 8 numbers.
+template <bool WT>
+__global__ void __launch_bounds__(128) k_heads_mma(const bf16* __restrict__ X, const bf16* __restrict__ Wt, bf16* __restrict__ Y, int N, int O, int K,
+                                                   HeadsGeom g) {
+  constexpr int KC = 64, LDX = KC + 8, LDW = WT ? 128 + 8 : KC + 8;
+  __shared__ __align__(16) bf16 Xs[64 * LDX];
+  __shared__ __align__(16) bf16 Ws[(WT ? KC : 128) * LDW];
+  const int z = blockIdx.z, n0 = blockIdx.y * 64, o0 = blockIdx.x * 128;
+  const bf16* Xz = X + (size_t)z * g.ldxz;
+  const bf16* Wz = Wt + (size_t)z * g.wz;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float acc[16][4];
+#pragma unroll
+  for (int j = 0; j < 16; j++) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += KC) {
+    __syncthreads();
+    for (int e = threadIdx.x; e < 64 * (KC / 8); e += 128) {
+      const int r = e / (KC / 8), c = (e % (KC / 8)) * 8;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (n0 + r < N && k0 + c < K) v = *reinterpret_cast<const uint4*>(Xz + (size_t)(n0 + r) * g.ldx + k0 + c);
+      *reinterpret_cast<uint4*>(Xs + r * LDX + c) = v;
+    }
+    if (WT) {
+      for (int e = threadIdx.x; e < KC * 16; e += 128) {
+        const int r = e / 16, c = (e % 16) * 8;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (k0 + r < K && o0 + c < O) v = *reinterpret_cast<const uint4*>(Wz + (size_t)(k0 + r) * g.wk + o0 + c);
+        *reinterpret_cast<uint4*>(Ws + r * LDW + c) = v;
+      }
+    } else {
+      for (int e = threadIdx.x; e < 128 * (KC / 8); e += 128) {
+        const int r = e / (KC / 8), c = (e % (KC / 8)) * 8;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (o0 + r < O && k0 + c < K) v = *reinterpret_cast<const uint4*>(Wz + (size_t)(o0 + r) * g.wo + k0 + c);
+        *reinterpret_cast<uint4*>(Ws + r * LDW + c) = v;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < KC / 16; kk++) {
+      uint32_t af[4];
+      ldsm_x4(af, Xs + (warp * 16 + (lane & 15)) * LDX + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+      for (int jj = 0; jj < 8; jj++) {
+        uint32_t bfr[4];
+        if (WT) ldsm_x4_t(bfr, Ws + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * LDW + jj * 16 + (lane >> 4) * 8);
+        else ldsm_x4(bfr, Ws + (jj * 16 + (lane >> 4) * 8 + (lane & 7)) * LDW + kk * 16 + ((lane >> 3) & 1) * 8);
+        mma_bf16(acc[2 * jj], af, bfr[0], bfr[1]);
+        mma_bf16(acc[2 * jj + 1], af, bfr[2], bfr[3]);
+      }
+    }
+  }
+  bf16* Yz = Y + (size_t)z * g.ldyz;
+  const int r0 = n0 + warp * 16 + (lane >> 2), r1 = r0 + 8;
+#pragma unroll
+  for (int j = 0; j < 16; j++) {
+    const int o = o0 + j * 8 + (lane & 3) * 2;
+    if (o < O) {      // O is even and the rows are 4-byte aligned (checked by the caller)
+      if (r0 < N) *reinterpret_cast<uint32_t*>(Yz + (size_t)r0 * g.ldy + o) = pack_bf16(acc[j][0], acc[j][1]);
+      if (r1 < N) *reinterpret_cast<uint32_t*>(Yz + (size_t)r1 * g.ldy + o) = pack_bf16(acc[j][2], acc[j][3]);
     }
   }
 }
