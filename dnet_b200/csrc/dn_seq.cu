@@ -675,27 +675,41 @@ static cudaError_t attn_tiles(cudaStream_t s, const Batch& b, const bf16* q, con
 
 // latent attention of a step that brings a prompt portion, bf16: the MMA tiles over the cached rows (R + rot numbers a key,
 // the first R the value) when the rows start on 16-byte boundaries
-static bool latent_tiles_ok(const Batch& b, int Ck, int R) { return b.max_len >= 16 && Ck % 8 == 0 && R % 2 == 0 && R <= 512; }
-template <int DVH>
+static bool latent_tiles_ok(const Batch& b, int Ck, int R) {
+  const int DKP = (Ck + 15) / 16 * 16, DVH = R <= 128 ? 64 : R <= 256 ? 128 : 256, LD = std::max(DKP, 2 * DVH) + 8;
+  return Ck % 8 == 0 && R % 2 == 0 && R <= 512 && (size_t)3 * 64 * LD * 2 <= g_max_smem;      // three tiles must fit the shared memory
+}
+template <int DVH, bool DEC>
 static cudaError_t latent_tiles_launch(cudaStream_t s, const Batch& b, const bf16* q, const bf16* pool, int H, int Ck, int R, int chunk, float scale,
-                                       const AttnExtra& ex, bf16* out) {
+                                       const AttnExtra& ex, bf16* out, float* part, int part_ld) {
   const int DKP = (Ck + 15) / 16 * 16, LD = std::max(DKP, 2 * DVH) + 8;
-  const size_t smem = (size_t)2 * 64 * LD * 2;
+  const size_t smem = (size_t)3 * 64 * LD * 2;      // the query tile and two key tiles
   static size_t attr = 0;
   if (smem > attr) {
-    cudaError_t e = cudaFuncSetAttribute(k_latent_tiles<DVH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(k_latent_tiles<DVH, DEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     attr = smem;
   }
   g_launches++;
-  k_latent_tiles<DVH><<<dim3(b.row_tiles, H), 256, smem, s>>>(b, q, pool, H, Ck, R, DKP, LD, chunk, scale, ex, out);
+  const dim3 grid = DEC ? dim3(b.N, (H + 63) / 64, AT_MAX_SPLITS) : dim3(b.row_tiles, H);
+  k_latent_tiles<DVH, DEC><<<grid, 256, smem, s>>>(b, q, pool, H, Ck, R, DKP, LD, chunk, scale, ex, out, part, part_ld);
   return cudaGetLastError();
 }
+// prompt portions: a block per (64 rows, head); decode steps (every entry one token): a block per (token, 64 heads, split) + the merge
 static cudaError_t latent_tiles(cudaStream_t s, const Batch& b, const bf16* q, const bf16* pool, int H, int Ck, int R, int chunk, float scale,
-                                const AttnExtra& ex, bf16* out) {
-  if (R <= 128) return latent_tiles_launch<64>(s, b, q, pool, H, Ck, R, chunk, scale, ex, out);
-  if (R <= 256) return latent_tiles_launch<128>(s, b, q, pool, H, Ck, R, chunk, scale, ex, out);
-  return latent_tiles_launch<256>(s, b, q, pool, H, Ck, R, chunk, scale, ex, out);
+                                const AttnExtra& ex, bf16* out, float* part, int part_ld) {
+  const bool dec = b.max_len == 1 && b.N <= AT_SPLIT_ROWS;
+  cudaError_t e;
+#define LT(D) (dec ? latent_tiles_launch<D, true>(s, b, q, pool, H, Ck, R, chunk, scale, ex, out, part, part_ld) \
+                   : latent_tiles_launch<D, false>(s, b, q, pool, H, Ck, R, chunk, scale, ex, out, part, part_ld))
+  if (R <= 128) e = LT(64);
+  else if (R <= 256) e = LT(128);
+  else e = LT(256);
+#undef LT
+  if (e != cudaSuccess || !dec) return e;
+  g_launches++;
+  k_latent_merge<<<dim3(b.N, H), 128, 0, s>>>(b, H, R, chunk, AT_MAX_SPLITS, ex, part, part_ld, out);
+  return cudaGetLastError();
 }
 
 // phase boundary: the time from this mark to the next one is booked on `phase`
@@ -981,8 +995,8 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
       // multi-query attention of all heads over the cached rows: keys [R + dr], values = their first R numbers
       PH(DN_SEQ_PH_ATTN);
       AttnExtra ex{lc.softcap, nullptr, lc.out_gate ? (const float*)m->pa : nullptr, lc.mask_kind == DN_MASK_WINDOW ? 1 : 0, l.Ck};
-      if (std::is_same<T, bf16>::value && latent_tiles_ok(b, l.Ck, R))
-        CK(latent_tiles(s, b, (const bf16*)m->qb, (const bf16*)pool, lc.heads, l.Ck, R, lc.chunk, lc.scale, ex, (bf16*)m->gt));
+      if (std::is_same<T, bf16>::value && latent_tiles_ok(b, l.Ck, R) && (b.max_len >= 16 || b.max_len == 1))
+        CK(latent_tiles(s, b, (const bf16*)m->qb, (const bf16*)pool, lc.heads, l.Ck, R, lc.chunk, lc.scale, ex, (bf16*)m->gt, m->attn_part, 2 + m->part_dv));
       else {
         const int Z = N <= AT_SPLIT_ROWS ? AT_MAX_SPLITS : 1;
         const size_t sm = (size_t)(((l.Ck + 3) & ~3) + AT_WARPS * (2 + (R + 31) / 32 * 32)) * 4;

@@ -210,55 +210,90 @@ __global__ void __launch_bounds__(256) k_upv_few(const T* __restrict__ X, const 
 // (w & 3) and the half (w >> 2) of the value columns -- with a latent of 512 the output accumulators of 16 rows x 256
 // columns are 128 registers a thread; both halves compute the same scores.  The query tile stays in shared memory
 // (its fragments are re-read per key tile: 576 numbers a row do not fit the registers beside the accumulators).
+// Shared memory holds the query tile and two key tiles (219 KB for a latent of 512 + 64): the next page is copied
+// (cp.async) while the current one is multiplied.
 // Scores, running maximum and sum are fp32; the weights enter P V as a bf16 pair (hi + lo).  Per row the key tiles are
 // visited in ascending position and a tile the row does not see changes nothing: the result does not depend on the cut.
 // DVH: value columns a warp owns (the block covers 2 DVH >= R).  LD: shared row pitch = max(padded key size, 2 DVH) + 8.
+//
+// DEC (decode steps): the 64 rows of a block are up to 64 *heads* of one token -- all heads read the same cached rows, so
+// a page is staged once for all of them -- and the pages a token sees are dealt round-robin to gridDim.z blocks, each
+// writing its partial (maximum, sum, unnormalised output) for k_latent_merge, which joins them in the order of z.
+// The split is a function of the token's own position.  grid (tokens, ceil(H / 64), splits).
+__device__ __forceinline__ int latent_splits(int p, int lo, int zmax) { return min(zmax, p / PAGE - lo / PAGE + 1); }
+// A 64-row tile into shared memory by asynchronous 16-byte copies (no registers, all of a thread's copies in flight at
+// once); rows >= valid and columns >= cols are filled with zeros (a copy of 0 source bytes).  The caller commits and waits.
+__device__ __forceinline__ void cp_async16(bf16* dst, const bf16* src, int src_bytes) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(src_bytes));
+}
 __device__ __forceinline__ void load_tile_rt(bf16* __restrict__ dst, const bf16* __restrict__ src, size_t ld, int cols, int valid, int LD) {
   const int vec = LD / 8 - 1;      // 16-byte groups per row, the pad group left out
   for (int e = threadIdx.x; e < 64 * vec; e += blockDim.x) {
     const int r = e / vec, c = (e % vec) * 8;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (r < valid && c < cols) v = *reinterpret_cast<const uint4*>(src + (size_t)r * ld + c);
-    *reinterpret_cast<uint4*>(dst + (size_t)r * LD + c) = v;
+    const bool in = r < valid && c < cols;
+    cp_async16(dst + (size_t)r * LD + c, in ? src + (size_t)r * ld + c : src, in ? 16 : 0);
   }
 }
-template <int DVH>
+template <int DVH, bool DEC>
 __global__ void __launch_bounds__(256, 1) k_latent_tiles(Batch b, const bf16* __restrict__ q, const bf16* __restrict__ kpool, int H, int Ck, int R,
-                                                         int DKP, int LD, int chunk, float scale, AttnExtra ex, bf16* __restrict__ out) {
+                                                         int DKP, int LD, int chunk, float scale, AttnExtra ex, bf16* __restrict__ out,
+                                                         float* __restrict__ part_g, int part_ld) {
   extern __shared__ __align__(16) unsigned char smraw[];
   bf16* Qs = reinterpret_cast<bf16*>(smraw);
-  bf16* Ks = Qs + 64 * LD;
-  int e = 0, t = blockIdx.x;
-  for (; e < b.E; e++) {
-    const int nt = (b.ent_start[e + 1] - b.ent_start[e] + 63) / 64;
-    if (t < nt) break;
-    t -= nt;
+  bf16* Kbuf = Qs + 64 * LD;      // two tiles
+  int e = 0, t = blockIdx.x, h = blockIdx.y, s0, rows, p_first, p_last, slot, page_step = PAGE, page0 = 0;
+  if (DEC) {
+    const int n = blockIdx.x;
+    h = blockIdx.y * 64;                        // first head of the block's rows
+    rows = min(64, H - h);
+    s0 = n;
+    p_first = p_last = b.pos[n];
+    slot = b.slot[n];
+    const int nz = latent_splits(p_last, attn_lo(p_last, chunk, ex.window), (int)gridDim.z);
+    if ((int)blockIdx.z >= nz) return;
+    page0 = blockIdx.z * PAGE;
+    page_step = nz * PAGE;
+  } else {
+    for (; e < b.E; e++) {
+      const int nt = (b.ent_start[e + 1] - b.ent_start[e] + 63) / 64;
+      if (t < nt) break;
+      t -= nt;
+    }
+    if (e >= b.E) return;
+    s0 = b.ent_start[e] + t * 64;
+    rows = min(64, b.ent_start[e + 1] - s0);
+    p_first = b.ent_pos0[e] + t * 64;
+    p_last = p_first + rows - 1;
+    slot = b.ent_slot[e];
   }
-  if (e >= b.E) return;
-  const int h = blockIdx.y;
-  const int s0 = b.ent_start[e] + t * 64, s1 = b.ent_start[e + 1];
-  const int rows = min(64, s1 - s0);
-  const int p_first = b.ent_pos0[e] + t * 64, p_last = p_first + rows - 1;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, rg = warp & 3, hv = warp >> 2;
-  load_tile_rt(Qs, q + ((size_t)s0 * H + h) * Ck, (size_t)H * Ck, Ck, rows, LD);
+  if (DEC) load_tile_rt(Qs, q + ((size_t)s0 * H + h) * Ck, (size_t)Ck, Ck, rows, LD);
+  else load_tile_rt(Qs, q + ((size_t)s0 * H + h) * Ck, (size_t)H * Ck, Ck, rows, LD);
   const int r0 = rg * 16 + (lane >> 2), r1 = r0 + 8;
-  const int p0 = r0 < rows ? p_first + r0 : -1, p1 = r1 < rows ? p_first + r1 : -1;
+  const int p0 = r0 < rows ? (DEC ? p_first : p_first + r0) : -1, p1 = r1 < rows ? (DEC ? p_first : p_first + r1) : -1;
   const int lo0 = p0 >= 0 ? attn_lo(p0, chunk, ex.window) : 0, lo1 = p1 >= 0 ? attn_lo(p1, chunk, ex.window) : 0;
   const bool warp_live = rg * 16 < rows;
   float o[DVH / 8][4];
 #pragma unroll
   for (int j = 0; j < DVH / 8; j++) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
-  const int32_t* bt = b.bt + (size_t)b.ent_slot[e] * b.max_pages;
+  const int32_t* bt = b.bt + (size_t)slot * b.max_pages;
   const int lo_tile = attn_lo(p_first, chunk, ex.window);
   const bf16* qrow = Qs + (size_t)(rg * 16 + (lane & 15)) * LD + (lane >> 4) * 8;
-  for (int j0 = (lo_tile / PAGE) * PAGE; j0 <= p_last; j0 += PAGE) {
-    const size_t prow = (size_t)bt[j0 / PAGE] * PAGE;
-    const int kvalid = min(PAGE, p_last - j0 + 1);
+  auto stage = [&](int j0, int buf) {      // rows of the page beyond the last query's position are not read
+    load_tile_rt(Kbuf + (size_t)buf * 64 * LD, kpool + (size_t)bt[j0 / PAGE] * PAGE * Ck, (size_t)Ck, Ck, min(PAGE, p_last - j0 + 1), LD);
+    cp_async_commit();
+  };
+  const int j_first = (lo_tile / PAGE) * PAGE + page0;
+  if (j_first <= p_last) stage(j_first, 0);      // (the query tile's copies are in this group too)
+  int buf = 0;
+  for (int j0 = j_first; j0 <= p_last; j0 += page_step, buf ^= 1) {
+    if (j0 + page_step <= p_last) { stage(j0 + page_step, buf ^ 1); cp_async_wait<1>(); }
+    else cp_async_wait<0>();
     __syncthreads();
-    load_tile_rt(Ks, kpool + prow * Ck, (size_t)Ck, Ck, kvalid, LD);
-    __syncthreads();
-    if (!warp_live) continue;
+    const bf16* Ks = Kbuf + (size_t)buf * 64 * LD;
+    if (!warp_live) { __syncthreads(); continue; }
     float sc[8][4];
 #pragma unroll
     for (int j = 0; j < 8; j++) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
@@ -332,8 +367,26 @@ __global__ void __launch_bounds__(256, 1) k_latent_tiles(Batch b, const bf16* __
         mma_bf16(o[2 * jj + 1], pl, vf[2], vf[3]);
       }
     }
+    __syncthreads();      // the tile is read out before the copy after next lands in it
   }
   if (!warp_live) return;
+  if (DEC) {      // the block's partial of every head: [maximum, sum, unnormalised output]
+    float* g0 = part_g + (((size_t)s0 * H + h + r0) * gridDim.z + blockIdx.z) * part_ld;
+    float* g1 = part_g + (((size_t)s0 * H + h + r1) * gridDim.z + blockIdx.z) * part_ld;
+    if (hv == 0 && (lane & 3) == 0) {
+      if (p0 >= 0) { g0[0] = m0; g0[1] = l0; }
+      if (p1 >= 0) { g1[0] = m1; g1[1] = l1; }
+    }
+#pragma unroll
+    for (int j = 0; j < DVH / 8; j++) {
+      const int d = hv * DVH + j * 8 + (lane & 3) * 2;
+      if (d < R) {
+        if (p0 >= 0) { g0[2 + d] = o[j][0]; g0[3 + d] = o[j][1]; }
+        if (p1 >= 0) { g1[2 + d] = o[j][2]; g1[3 + d] = o[j][3]; }
+      }
+    }
+    return;
+  }
   float i0 = p0 >= 0 ? 1.f / l0 : 0.f, i1 = p1 >= 0 ? 1.f / l1 : 0.f;
   if (ex.gate) {
     if (p0 >= 0) i0 *= sigmoid_f(ex.gate[(size_t)(s0 + r0) * H + h]);
@@ -346,6 +399,27 @@ __global__ void __launch_bounds__(256, 1) k_latent_tiles(Batch b, const bf16* __
       if (p0 >= 0) *reinterpret_cast<uint32_t*>(out + ((size_t)(s0 + r0) * H + h) * R + d) = pack_bf16(o[j][0] * i0, o[j][1] * i0);
       if (p1 >= 0) *reinterpret_cast<uint32_t*>(out + ((size_t)(s0 + r1) * H + h) * R + d) = pack_bf16(o[j][2] * i1, o[j][3] * i1);
     }
+  }
+}
+
+// joins the partials of k_latent_tiles<., true> in the order of the splits, applies the head's gate; grid (tokens, H)
+__global__ void k_latent_merge(Batch b, int H, int R, int chunk, int zmax, AttnExtra ex, const float* __restrict__ part_g, int part_ld,
+                               bf16* __restrict__ out) {
+  const int n = blockIdx.x, h = blockIdx.y, p = b.pos[n];
+  const int nz = latent_splits(p, attn_lo(p, chunk, ex.window), zmax);
+  const float* pg = part_g + ((size_t)n * H + h) * zmax * part_ld;
+  const float og = ex.gate ? sigmoid_f(ex.gate[(size_t)n * H + h]) : 1.f;
+  float M = -INFINITY;
+  for (int z = 0; z < nz; z++) M = fmaxf(M, pg[(size_t)z * part_ld]);
+  for (int d = threadIdx.x; d < R; d += blockDim.x) {
+    float L = 0.f, a = 0.f;
+    for (int z = 0; z < nz; z++) {
+      const float* pz = pg + (size_t)z * part_ld;
+      const float f = expf(pz[0] - M);
+      L += pz[1] * f;
+      a += pz[2 + d] * f;
+    }
+    out[((size_t)n * H + h) * R + d] = __float2bfloat16_rn(a / L * og);
   }
 }
 
