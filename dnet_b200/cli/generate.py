@@ -1,4 +1,4 @@
-"""Generate from a layer-list model (Moputar, Filinex) with the continuous-batching token loop.
+"""Generate from a layer-list model (Moputar, Filinex, Lutesun) with the continuous-batching token loop.
 
     bin/generate --model DIR [--dtype bfloat16|float32] [--max-new-tokens N] [--temperature T] [--top-p P] [--top-k K]
                  [--max-tokens N] [--max-seqs S] [--step-tokens B] [--seed X]
