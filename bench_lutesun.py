@@ -13,7 +13,7 @@ from __future__ import annotations
 from bench_filinex import _run_filinex, filinex_algorithmic
 from bench_seqmix import HD, SIZES, VOCAB, _Flusher, _rand, _roofline, _timed
 
-EXPERTS, IDENTITY, TOP = 16, 2, 2
+EXPERTS, IDENTITY, TOP = 16, 4, 2
 ROT, KV_RANK, WINDOW = 64, 512, 1024
 
 
@@ -22,7 +22,7 @@ def lutesun_config(sz: dict) -> dict:
     unrotated + 64 rotated query dims and 128 value dims over a latent of 512 (a cached row of 576 numbers a token
     and layer); active feed-forward width = top x expert width + shared width = the dense width of the size."""
     W, H, ff = sz["width"], sz["heads"], sz["ff"]
-    moe = {"kind": "moe", "router": {"experts": EXPERTS, "top": TOP, "identity": IDENTITY, "scale": 2.5, "groups": {"count": 2, "keep": 1}},
+    moe = {"kind": "moe", "router": {"experts": EXPERTS, "top": TOP, "identity": IDENTITY, "scale": 2.0, "groups": {"count": 4, "keep": 2}},
            "expert": {"ff": ff // 4}, "shared": {"ff": ff // 2}}
     mx = {"heads": H, "dim": HD, "rot_dim": ROT, "vdim": HD, "kv_rank": KV_RANK, "scale": (HD + ROT) ** -0.5, "rot": {"base": 10000.0, "dims": ROT},
           "mask": {"size": WINDOW}}

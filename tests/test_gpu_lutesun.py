@@ -211,14 +211,14 @@ def test_sizes_that_allow_no_wide_loads(dtype):
 LAYER_SIZED = {
     # width 384: expert width 96 has no TMA descriptor, the others do
     "w384": config([lat({"kind": "dense", "ff": 640}, heads=6, dim=64, rot_dim=32, vdim=64, kv_rank=128, mask={"size": 90}),
-                    lat({"kind": "moe", "router": {"experts": 8, "top": 3, "identity": 0, "scale": 2.5, "groups": {"count": 4, "keep": 2}}, "expert": {"ff": 96},
+                    lat({"kind": "moe", "router": {"experts": 8, "top": 3, "identity": 0, "scale": 0.8, "groups": {"count": 4, "keep": 2}}, "expert": {"ff": 96},
                          "shared": {"ff": 160}}, second=True, heads=12, dim=32, rot_dim=16, vdim=48, kv_rank=64, q_rank=192, mask={"size": 128}),
                     lat(None, heads=4, dim=48, rot_dim=16, vdim=80, kv_rank=256, mask={"size": 40})], width=384, vocab=640),
     # width 512, 32 experts in 8 groups, latent of 320 (the wider value accumulators of the decode kernel)
     "w512": config([lat({"kind": "moe", "router": {"experts": 30, "top": 4, "identity": 2, "scale": 1.0, "groups": {"count": 8, "keep": 4}}, "expert": {"ff": 128},
                          "shared": None}, heads=8, dim=64, rot_dim=64, vdim=64, kv_rank=320, mask={"size": 300}),
                     lat({"kind": "dense", "ff": 1024}, second=True, heads=8, dim=64, rot_dim=32, vdim=32, kv_rank=128, q_rank=256, mask={"size": 64}),
-                    lat({"kind": "moe", "router": {"experts": 16, "top": 2, "identity": 0, "scale": 2.5}, "expert": {"ff": 64}, "shared": {"ff": 192}},
+                    lat({"kind": "moe", "router": {"experts": 16, "top": 3, "identity": 0, "scale": 1.5}, "expert": {"ff": 64}, "shared": {"ff": 192}},
                         heads=16, dim=32, rot_dim=32, vdim=32, kv_rank=64, mask={"size": 17})], width=512, vocab=1000),
 }
 
