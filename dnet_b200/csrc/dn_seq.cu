@@ -679,36 +679,40 @@ static bool latent_tiles_ok(const Batch& b, int Ck, int R) {
   const int DKP = (Ck + 15) / 16 * 16, DVH = R <= 128 ? 64 : R <= 256 ? 128 : 256, LD = std::max(DKP, 2 * DVH) + 8;
   return Ck % 8 == 0 && R % 2 == 0 && R <= 512 && (size_t)3 * 64 * LD * 2 <= g_max_smem;      // three tiles must fit the shared memory
 }
-template <int DVH, bool DEC>
+template <int DVH, int MODE>
 static cudaError_t latent_tiles_launch(cudaStream_t s, const Batch& b, const bf16* q, const bf16* pool, int H, int Ck, int R, int chunk, float scale,
-                                       const AttnExtra& ex, bf16* out, float* part, int part_ld) {
+                                       const AttnExtra& ex, bf16* out, float* part, int part_ld, int zmax) {
   const int DKP = (Ck + 15) / 16 * 16, LD = std::max(DKP, 2 * DVH) + 8;
   const size_t smem = (size_t)3 * 64 * LD * 2;      // the query tile and two key tiles
   static size_t attr = 0;
   if (smem > attr) {
-    cudaError_t e = cudaFuncSetAttribute(k_latent_tiles<DVH, DEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(k_latent_tiles<DVH, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     attr = smem;
   }
   g_launches++;
-  const dim3 grid = DEC ? dim3(b.N, (H + 63) / 64, AT_MAX_SPLITS) : dim3(b.row_tiles, H);
-  k_latent_tiles<DVH, DEC><<<grid, 256, smem, s>>>(b, q, pool, H, Ck, R, DKP, LD, chunk, scale, ex, out, part, part_ld);
+  const dim3 grid = MODE ? dim3(b.N, (H + 63) / 64, zmax) : dim3(b.row_tiles, H);
+  k_latent_tiles<DVH, MODE><<<grid, 256, smem, s>>>(b, q, pool, H, Ck, R, DKP, LD, chunk, scale, ex, out, part, part_ld);
   return cudaGetLastError();
 }
-// prompt portions: a block per (64 rows, head); decode steps (every entry one token): a block per (token, 64 heads, split) + the merge
+// prompt portions: a block per (64 rows, head); decode steps (every entry one token): a block per (token, 64 heads, split) + the merge.
+// The partials' buffer holds AT_SPLIT_ROWS x AT_MAX_SPLITS rows per head: up to 8 tokens are split 32 ways, more 16 ways.
 static cudaError_t latent_tiles(cudaStream_t s, const Batch& b, const bf16* q, const bf16* pool, int H, int Ck, int R, int chunk, float scale,
                                 const AttnExtra& ex, bf16* out, float* part, int part_ld) {
   const bool dec = b.max_len == 1 && b.N <= AT_SPLIT_ROWS;
+  const int zmax = b.N <= 8 ? 32 : AT_MAX_SPLITS;
+  const int mode = !dec ? 0 : H <= 16 ? 2 : 1;
   cudaError_t e;
-#define LT(D) (dec ? latent_tiles_launch<D, true>(s, b, q, pool, H, Ck, R, chunk, scale, ex, out, part, part_ld) \
-                   : latent_tiles_launch<D, false>(s, b, q, pool, H, Ck, R, chunk, scale, ex, out, part, part_ld))
+#define LT(D) (mode == 0 ? latent_tiles_launch<D, 0>(s, b, q, pool, H, Ck, R, chunk, scale, ex, out, part, part_ld, zmax) \
+             : mode == 1 ? latent_tiles_launch<D, 1>(s, b, q, pool, H, Ck, R, chunk, scale, ex, out, part, part_ld, zmax) \
+                         : latent_tiles_launch<D, 2>(s, b, q, pool, H, Ck, R, chunk, scale, ex, out, part, part_ld, zmax))
   if (R <= 128) e = LT(64);
   else if (R <= 256) e = LT(128);
   else e = LT(256);
 #undef LT
   if (e != cudaSuccess || !dec) return e;
   g_launches++;
-  k_latent_merge<<<dim3(b.N, H), 128, 0, s>>>(b, H, R, chunk, AT_MAX_SPLITS, ex, part, part_ld, out);
+  k_latent_merge<<<dim3(b.N, H), 128, 0, s>>>(b, H, R, chunk, zmax, ex, part, part_ld, out);
   return cudaGetLastError();
 }
 

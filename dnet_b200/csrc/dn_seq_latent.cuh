@@ -219,7 +219,9 @@ __global__ void __launch_bounds__(256) k_upv_few(const T* __restrict__ X, const 
 // DEC (decode steps): the 64 rows of a block are up to 64 *heads* of one token -- all heads read the same cached rows, so
 // a page is staged once for all of them -- and the pages a token sees are dealt round-robin to gridDim.z blocks, each
 // writing its partial (maximum, sum, unnormalised output) for k_latent_merge, which joins them in the order of z.
-// The split is a function of the token's own position.  grid (tokens, ceil(H / 64), splits).
+// The split is a function of the token's own position.  grid (tokens, ceil(H / 64), splits).  MODE 1: up to 64 heads a
+// block, warps as for prompts; MODE 2 (at most 16 heads): one row group, so all eight warps take an eighth of the value
+// columns each (every warp computes the 16 x 64 scores).
 __device__ __forceinline__ int latent_splits(int p, int lo, int zmax) { return min(zmax, p / PAGE - lo / PAGE + 1); }
 // A 64-row tile into shared memory by asynchronous 16-byte copies (no registers, all of a thread's copies in flight at
 // once); rows >= valid and columns >= cols are filled with zeros (a copy of 0 source bytes).  The caller commits and waits.
@@ -235,10 +237,12 @@ __device__ __forceinline__ void load_tile_rt(bf16* __restrict__ dst, const bf16*
     cp_async16(dst + (size_t)r * LD + c, in ? src + (size_t)r * ld + c : src, in ? 16 : 0);
   }
 }
-template <int DVH, bool DEC>
+template <int DVH, int MODE>
 __global__ void __launch_bounds__(256, 1) k_latent_tiles(Batch b, const bf16* __restrict__ q, const bf16* __restrict__ kpool, int H, int Ck, int R,
                                                          int DKP, int LD, int chunk, float scale, AttnExtra ex, bf16* __restrict__ out,
                                                          float* __restrict__ part_g, int part_ld) {
+  constexpr bool DEC = MODE != 0;
+  constexpr int CW = MODE == 2 ? DVH / 4 : DVH;      // value columns a warp owns
   extern __shared__ __align__(16) unsigned char smraw[];
   bf16* Qs = reinterpret_cast<bf16*>(smraw);
   bf16* Kbuf = Qs + 64 * LD;      // two tiles
@@ -267,16 +271,16 @@ __global__ void __launch_bounds__(256, 1) k_latent_tiles(Batch b, const bf16* __
     p_last = p_first + rows - 1;
     slot = b.ent_slot[e];
   }
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, rg = warp & 3, hv = warp >> 2;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, rg = MODE == 2 ? 0 : (warp & 3), hv = MODE == 2 ? warp : (warp >> 2);
   if (DEC) load_tile_rt(Qs, q + ((size_t)s0 * H + h) * Ck, (size_t)Ck, Ck, rows, LD);
   else load_tile_rt(Qs, q + ((size_t)s0 * H + h) * Ck, (size_t)H * Ck, Ck, rows, LD);
   const int r0 = rg * 16 + (lane >> 2), r1 = r0 + 8;
   const int p0 = r0 < rows ? (DEC ? p_first : p_first + r0) : -1, p1 = r1 < rows ? (DEC ? p_first : p_first + r1) : -1;
   const int lo0 = p0 >= 0 ? attn_lo(p0, chunk, ex.window) : 0, lo1 = p1 >= 0 ? attn_lo(p1, chunk, ex.window) : 0;
   const bool warp_live = rg * 16 < rows;
-  float o[DVH / 8][4];
+  float o[CW / 8][4];
 #pragma unroll
-  for (int j = 0; j < DVH / 8; j++) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+  for (int j = 0; j < CW / 8; j++) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
   const int32_t* bt = b.bt + (size_t)slot * b.max_pages;
   const int lo_tile = attn_lo(p_first, chunk, ex.window);
@@ -344,7 +348,7 @@ __global__ void __launch_bounds__(256, 1) k_latent_tiles(Batch b, const bf16* __
     l0 = l0 * c0 + ps0; l1 = l1 * c1 + ps1;
     m0 = n0; m1 = n1;
 #pragma unroll
-    for (int j = 0; j < DVH / 8; j++) { o[j][0] *= c0; o[j][1] *= c0; o[j][2] *= c1; o[j][3] *= c1; }
+    for (int j = 0; j < CW / 8; j++) { o[j][0] *= c0; o[j][1] *= c0; o[j][2] *= c1; o[j][3] *= c1; }
     // O += P V with P = hi + lo; V = the first columns of the key tile
 #pragma unroll
     for (int kk = 0; kk < 4; kk++) {
@@ -356,9 +360,9 @@ __global__ void __launch_bounds__(256, 1) k_latent_tiles(Batch b, const bf16* __
         ph[x] = pack_bf16(ah, ch);
         pl[x] = pack_bf16(a - ah, c - ch);
       }
-      const bf16* vrow = Ks + (size_t)(kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * LD + hv * DVH + (lane >> 4) * 8;
+      const bf16* vrow = Ks + (size_t)(kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * LD + hv * CW + (lane >> 4) * 8;
 #pragma unroll
-      for (int jj = 0; jj < DVH / 16; jj++) {
+      for (int jj = 0; jj < CW / 16; jj++) {
         uint32_t vf[4];
         ldsm_x4_t(vf, vrow + jj * 16);
         mma_bf16(o[2 * jj], ph, vf[0], vf[1]);
@@ -378,8 +382,8 @@ __global__ void __launch_bounds__(256, 1) k_latent_tiles(Batch b, const bf16* __
       if (p1 >= 0) { g1[0] = m1; g1[1] = l1; }
     }
 #pragma unroll
-    for (int j = 0; j < DVH / 8; j++) {
-      const int d = hv * DVH + j * 8 + (lane & 3) * 2;
+    for (int j = 0; j < CW / 8; j++) {
+      const int d = hv * CW + j * 8 + (lane & 3) * 2;
       if (d < R) {
         if (p0 >= 0) { g0[2 + d] = o[j][0]; g0[3 + d] = o[j][1]; }
         if (p1 >= 0) { g1[2 + d] = o[j][2]; g1[3 + d] = o[j][3]; }
@@ -393,8 +397,8 @@ __global__ void __launch_bounds__(256, 1) k_latent_tiles(Batch b, const bf16* __
     if (p1 >= 0) i1 *= sigmoid_f(ex.gate[(size_t)(s0 + r1) * H + h]);
   }
 #pragma unroll
-  for (int j = 0; j < DVH / 8; j++) {
-    const int d = hv * DVH + j * 8 + (lane & 3) * 2;
+  for (int j = 0; j < CW / 8; j++) {
+    const int d = hv * CW + j * 8 + (lane & 3) * 2;
     if (d < R) {
       if (p0 >= 0) *reinterpret_cast<uint32_t*>(out + ((size_t)(s0 + r0) * H + h) * R + d) = pack_bf16(o[j][0] * i0, o[j][1] * i0);
       if (p1 >= 0) *reinterpret_cast<uint32_t*>(out + ((size_t)(s0 + r1) * H + h) * R + d) = pack_bf16(o[j][2] * i1, o[j][3] * i1);
@@ -402,24 +406,34 @@ __global__ void __launch_bounds__(256, 1) k_latent_tiles(Batch b, const bf16* __
   }
 }
 
-// joins the partials of k_latent_tiles<., true> in the order of the splits, applies the head's gate; grid (tokens, H)
+// joins the partials of k_latent_tiles<., true> in the order of the splits, applies the head's gate; grid (tokens, H).
+// One warp turns the splits' maxima and sums into a weight per split; every thread then adds its value numbers over
+// the splits with all loads in flight at once (zmax <= 32).
 __global__ void k_latent_merge(Batch b, int H, int R, int chunk, int zmax, AttnExtra ex, const float* __restrict__ part_g, int part_ld,
                                bf16* __restrict__ out) {
+  __shared__ float f[32];
+  __shared__ float scale;
   const int n = blockIdx.x, h = blockIdx.y, p = b.pos[n];
   const int nz = latent_splits(p, attn_lo(p, chunk, ex.window), zmax);
   const float* pg = part_g + ((size_t)n * H + h) * zmax * part_ld;
-  const float og = ex.gate ? sigmoid_f(ex.gate[(size_t)n * H + h]) : 1.f;
-  float M = -INFINITY;
-  for (int z = 0; z < nz; z++) M = fmaxf(M, pg[(size_t)z * part_ld]);
+  if (threadIdx.x < 32) {
+    const int z = threadIdx.x;
+    const float m = z < nz ? pg[(size_t)z * part_ld] : -INFINITY;
+    const float M = warp_max(m);
+    const float fz = z < nz ? expf(m - M) : 0.f;
+    const float L = warp_sum(z < nz ? pg[(size_t)z * part_ld + 1] * fz : 0.f);
+    f[z] = fz;
+    if (z == 0) scale = (ex.gate ? sigmoid_f(ex.gate[(size_t)n * H + h]) : 1.f) / L;
+  }
+  __syncthreads();
   for (int d = threadIdx.x; d < R; d += blockDim.x) {
-    float L = 0.f, a = 0.f;
-    for (int z = 0; z < nz; z++) {
-      const float* pz = pg + (size_t)z * part_ld;
-      const float f = expf(pz[0] - M);
-      L += pz[1] * f;
-      a += pz[2 + d] * f;
-    }
-    out[((size_t)n * H + h) * R + d] = __float2bfloat16_rn(a / L * og);
+    float v[32];
+#pragma unroll
+    for (int z = 0; z < 32; z++) v[z] = z < nz ? pg[(size_t)z * part_ld + 2 + d] : 0.f;
+    float a = 0.f;
+#pragma unroll
+    for (int z = 0; z < 32; z++) a = fmaf(v[z], f[z], a);
+    out[((size_t)n * H + h) * R + d] = __float2bfloat16_rn(a * scale);
   }
 }
 
