@@ -426,6 +426,25 @@ def test_long_rows_split_over_blocks_in_decoding():
             assert err(lg[first:], ref[first:first + n]) < TOL["float32"]
 
 
+@pytest.mark.parametrize("heads", [17, 20, 64, 70])
+def test_many_heads_in_decoding(heads):
+    """bf16 decode steps put the heads of a token into the rows of one MMA tile: more than 16 heads fill several row
+    groups, more than 64 several blocks; beside it the same model in prompts and in fp32"""
+    cfg = config([lat(heads=heads, dim=8, rot_dim=8, vdim=8, kv_rank=24, mask={"size": 150}),
+                  lat(DENSE, second=True, heads=heads, dim=8, rot_dim=8, vdim=8, kv_rank=16, q_rank=32, mask={"size": 70})])
+    t = toks(200, seed=170 + heads)
+    for dtype in ("bfloat16", "float32"):
+        with Rig(cfg, dtype, seed=heads) as rig:
+            ref = rig.oracle(t)
+            e = err16 if dtype == "bfloat16" else err
+            assert e(run_schedule(rig, t, [140]), ref) < TOL[dtype]
+            a, b = t[:90], t[5:130]                                          # two sequences decoding side by side
+            rig.eng.step([("a", a[:80], []), ("b", b[:120], [])])
+            got = [rig.eng.step([("a", [a[80 + i]], [0]), ("b", [b[120 + i]], [0])]) for i in range(5)]
+            ga, gb = torch.cat([g[:1] for g in got]), torch.cat([g[1:] for g in got])
+            assert e(ga, rig.oracle(a[:85])[80:]) < TOL[dtype] and e(gb, rig.oracle(b[:125])[120:]) < TOL[dtype]
+
+
 def test_first_tokens_of_a_sequence():
     with Rig(FULL, "float32") as rig:
         for n in (1, 2, 3, 4):
