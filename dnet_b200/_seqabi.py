@@ -17,7 +17,9 @@ DN_SEQ_BF16, DN_SEQ_F32 = 0, 1
 DN_MIX_ATTENTION, DN_MIX_DELTA, DN_MIX_PARALLEL, DN_MIX_WKV, DN_MIX_LATENT = 0, 1, 2, 3, 4
 DN_MASK_BLOCK, DN_MASK_WINDOW = 0, 1
 DN_ROT_INTERLEAVED, DN_ROT_HALF = 0, 1
-DN_NORM_RMS, DN_NORM_DYT = 0, 1
+DN_NORM_RMS, DN_NORM_DYT, DN_NORM_LAYER = 0, 1, 2
+DN_QKNORM_NONE, DN_QKNORM_WHOLE, DN_QKNORM_HEAD = 0, 1, 2
+DN_RIGHT_GLA, DN_RIGHT_GDELTA = 0, 1
 DN_MLP_DENSE, DN_MLP_MOE = 0, 1
 DN_FF_GEGLU, DN_FF_RELU2 = 0, 1
 DN_ROUTER_TOPK, DN_ROUTER_SCORED = 0, 1
@@ -34,15 +36,16 @@ _LAYER_SLOTS = ["norm1", "norm2", "mix.q", "mix.k", "mix.v", "mix.o", "mix.q.con
                 "mu.r", "mu.k", "mu.v", "mu.g", "mu.w", "bonus",
                 "router", "router.b", "shared.gate", "shared.up", "shared.down",
                 "mix.dq", "mix.dq.norm", "mix.dkv", "mix.dkv.norm", "mix.uk", "mix.uv",
-                "mlp.up.b", "mlp.down.b", "router.corr", "shared.sg"]
+                "mlp.up.b", "mlp.down.b", "router.corr", "shared.sg",
+                "canon1", "canon2", "l.out", "r.out", "r.a", "r.ab"]
 LAYER_SLOT = {n: i for i, n in enumerate(_LAYER_SLOTS)}
 MODEL_SLOT = {"embed": 100, "final.norm": 101, "head": 102, "final.norm.b": 103, "final.norm.alpha": 104,
-              "embed.norm": 105, "embed.norm.b": 106, "embed.norm.alpha": 107, "loop.in": 108}
+              "embed.norm": 105, "embed.norm.b": 106, "embed.norm.alpha": 107, "loop.in": 108, "bigram": 109}
 EXPERT_SLOT = {"gate": 0, "up": 1, "down": 2}
 # phases of a step, in the header's order (dn_seq_profile_read)
 PHASES = ["embed", "norm", "proj", "attn_prep", "attn", "delta_prep", "delta_rule", "delta_out", "conv_carry", "out_proj",
           "write_back", "ff_up", "ff_down", "head", "other", "recur_prep", "recur", "recur_out", "router", "moe_up", "moe_down",
-          "latent_in", "latent_out"]
+          "latent_in", "latent_out", "canon"]
 
 
 class LayerCfg(C.Structure):
@@ -56,7 +59,10 @@ class LayerCfg(C.Structure):
                 ("shared_ff", C.c_int32), ("shared_limit", C.c_float),
                 ("mask_kind", C.c_int32), ("rot_layout", C.c_int32), ("kv_rank", C.c_int32), ("q_rank", C.c_int32), ("rot_part", C.c_int32),
                 ("ff_act", C.c_int32), ("router_kind", C.c_int32), ("expert_act", C.c_int32), ("identity", C.c_int32),
-                ("groups", C.c_int32), ("groups_keep", C.c_int32), ("router_scale", C.c_float), ("shared_gate", C.c_int32)]
+                ("groups", C.c_int32), ("groups_keep", C.c_int32), ("router_scale", C.c_float), ("shared_gate", C.c_int32),
+                ("v_is_k", C.c_int32), ("qtemp_coef", C.c_float), ("qtemp_every", C.c_int32), ("pool", C.c_int32),
+                ("yarn_factor", C.c_float), ("yarn_original", C.c_float), ("yarn_fast", C.c_float), ("yarn_slow", C.c_float),
+                ("r_kind", C.c_int32), ("branch_norm", C.c_int32)]
 
 
 class SeqCfg(C.Structure):
@@ -64,7 +70,9 @@ class SeqCfg(C.Structure):
                 ("eps", C.c_float), ("embed_scale", C.c_float), ("pool_pages", C.c_int32), ("max_seqs", C.c_int32),
                 ("max_batch_tokens", C.c_int32),
                 ("norm_kind", C.c_int32), ("post_norm", C.c_int32), ("embed_norm", C.c_int32), ("logit_softcap", C.c_float),
-                ("loop_start", C.c_int32), ("loop_stop", C.c_int32), ("loop_times", C.c_int32), ("no_pre_norm", C.c_int32)]
+                ("loop_start", C.c_int32), ("loop_stop", C.c_int32), ("loop_times", C.c_int32), ("no_pre_norm", C.c_int32),
+                ("canon_taps", C.c_int32), ("bigram_buckets", C.c_int32), ("bigram_mul_prev", C.c_int32), ("bigram_mul_cur", C.c_int32),
+                ("logit_scale", C.c_float)]
 
 
 def declared_symbols() -> List[str]:

@@ -3,7 +3,7 @@ from typing import Any, List, Optional
 
 from .base import BaseRingModel, KVHandle
 from .llama import LlamaRingModel, MixtralRingModel, Qwen2RingModel
-from .seqmix import FilinexRingModel, LutesunRingModel, MoputarRingModel, SeqHandle, SeqMixRingModel
+from .seqmix import FilinexRingModel, LutesunRingModel, MoputarRingModel, SeqHandle, SeqMixRingModel, VulanexRingModel
 
 
 def _subclasses(cls):
@@ -30,4 +30,4 @@ def get_ring_model(model_type: str, model_config: Any, assigned_layers: Optional
 
 
 __all__ = ["BaseRingModel", "FilinexRingModel", "KVHandle", "LlamaRingModel", "LutesunRingModel", "MixtralRingModel", "MoputarRingModel", "Qwen2RingModel", "SeqHandle",
-           "SeqMixRingModel", "get_ring_model", "ring_model_class"]
+           "SeqMixRingModel", "VulanexRingModel", "get_ring_model", "ring_model_class"]

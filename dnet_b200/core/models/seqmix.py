@@ -43,6 +43,19 @@ read from the checkpoint's tensor shapes (``tensor_shapes``), or from the option
                  "mlp": {"kind": "dense", "ff": F}
                       | {"kind": "moe", "router": {"experts", "top", "identity", "scale", "groups": {"count", "keep"}},
                          "expert": {"ff"}, "shared": {"ff"} | null} | null}, ...]}
+
+``VulanexRingModel``: layer norms, a causal convolution on every sublayer's input, a hashed bigram row in the embedding,
+attention whose values are its keys beside layers that run windowed attention with pooled blocks next to a generalized
+delta rule:
+
+    {"architecture": "Vulanex", "vocab": V, "width": W, "norm": {"eps": e}, "logit_scale": c, "canon": {"taps": n},
+     "embedding": {"bigram": {"buckets", "mul_prev", "mul_cur"}},
+     "layers": [{"type": "attention",
+                 "mixer": {"heads", "kv_heads", "dim", "vdim", "scale", "q_temp": {"coef", "every"}}, "mlp": ...},
+                {"type": "parallel",
+                 "mixer": {"left": {"heads", "kv_heads", "dim", "vdim", "scale", "mask": {"size", "pool"},
+                                    "rot": {"base", "dims", "scaling": {"factor", "original", "fast", "slow"}}},
+                           "right": {"heads", "dim"}}, "mlp": ...}, ...]}
 """
 from __future__ import annotations
 
@@ -79,15 +92,24 @@ class SeqHandle:
         self.slot = -1
 
 
-def _attention_cfg(lc: _seqabi.LayerCfg, mx: dict, qk_norm: bool, mask: str = "block") -> None:
+def _attention_cfg(lc: _seqabi.LayerCfg, mx: dict, qk_norm, mask: str = "block", rot_layout: str = "interleaved") -> None:
     lc.scale = float(mx.get("scale", float(mx["dim"]) ** -0.5))
     lc.chunk = int((mx.get("mask") or {}).get("size", 0))
     lc.mask_kind = _seqabi.DN_MASK_WINDOW if mask == "window" else _seqabi.DN_MASK_BLOCK
+    lc.pool = int((mx.get("mask") or {}).get("pool", 0) or 0) if mask == "window" else 0
     rot = mx.get("rot") or {}
     lc.rot_dims = int(rot.get("dims", 0))
     lc.rot_base = float(rot.get("base", 10000.0))
+    lc.rot_layout = _seqabi.DN_ROT_HALF if rot_layout == "half" else _seqabi.DN_ROT_INTERLEAVED
+    sc = rot.get("scaling")
+    if sc:
+        lc.yarn_factor, lc.yarn_original = float(sc["factor"]), float(sc["original"])
+        lc.yarn_fast, lc.yarn_slow = float(sc["fast"]), float(sc["slow"])
+    qt = mx.get("q_temp")
+    if qt:
+        lc.qtemp_coef, lc.qtemp_every = float(qt["coef"]), int(qt["every"])
     lc.kv_from = int(mx["kv_from"]) if mx.get("kv_from") is not None else -1
-    lc.qk_norm = int(qk_norm)
+    lc.qk_norm = _seqabi.DN_QKNORM_HEAD if qk_norm == "head" else int(bool(qk_norm))
     lc.softcap = float(mx.get("softcap", 0.0) or 0.0)
     lc.heads, lc.kv_heads = int(mx["heads"]), int(mx.get("kv_heads", mx["heads"]))
     lc.dim, lc.vdim = int(mx["dim"]), int(mx.get("vdim", mx["dim"]))
@@ -101,8 +123,14 @@ def parse_layer_list(cfg: dict, family: Optional[dict] = None,
     sublayer and on the embedding, whether attention norms q and k, has a sink, gates its heads)."""
     fam = {"norm": "rms", "post_norm": False, "pre_norm": True, "embed_norm": False, "qk_norm": True, "sink": False, "head_gate": False,
            "mask": "block", "ff_act": "geglu", "router": "topk", "expert_act": "cglu", "shared_gate": False}
+    fam.update({"v_is_k": False, "rot_layout": "interleaved", "right": "gla", "branch_norm": False})
     fam.update(family or {})
     shapes = shapes or {}
+
+    def per(key: str, kind: str):
+        """a family's setting, which may differ by layer type ({type: value}; absent types are off)"""
+        v = fam[key]
+        return v.get(kind, False) if isinstance(v, dict) else v
 
     def from_shape(name: str, axis: int, mx: dict, key: str, what: str) -> int:
         if mx.get(key) is not None:
@@ -119,8 +147,8 @@ def parse_layer_list(cfg: dict, family: Optional[dict] = None,
         lc.kv_from = -1
         if kind == "attention":
             lc.mixer = _seqabi.DN_MIX_ATTENTION
-            _attention_cfg(lc, mx, fam["qk_norm"], fam["mask"])
-            lc.sink, lc.out_gate = int(fam["sink"]), int(fam["head_gate"])
+            _attention_cfg(lc, mx, per("qk_norm", kind), fam["mask"], fam["rot_layout"])
+            lc.sink, lc.out_gate, lc.v_is_k = int(per("sink", kind)), int(per("head_gate", kind)), int(per("v_is_k", kind))
         elif kind in ("latent_attention", "latent_attention_2"):
             # the second type sends its queries through a normed latent too, pairs rotary dims half apart and gates its heads
             second = kind == "latent_attention_2"
@@ -138,13 +166,19 @@ def parse_layer_list(cfg: dict, family: Optional[dict] = None,
             lc.conv = int(mx.get("conv", 0) or 0)
         elif kind == "parallel":
             lc.mixer = _seqabi.DN_MIX_PARALLEL
-            _attention_cfg(lc, mx["left"], fam["qk_norm"])
-            lc.sink, lc.out_gate = int(fam["sink"]), int(fam["head_gate"])
+            _attention_cfg(lc, mx["left"], per("qk_norm", kind), fam["mask"] if fam["right"] == "gdelta" else "block", fam["rot_layout"])
+            lc.sink, lc.out_gate = int(per("sink", kind)), int(per("head_gate", kind))
             r = mx["right"]
             lc.r_heads, lc.r_dim, lc.r_vdim = int(r["heads"]), int(r["dim"]), int(r.get("vdim", r["dim"]))
-            lc.tau = float(r["tau"])
-            lc.rank = from_shape(f"l{i}.mix.right.a1", 0, r, "rank", f"layer {i}")
-            lc.left_scale, lc.right_scale = float(mx.get("left_scale", 1.0)), float(mx.get("right_scale", 1.0))
+            if fam["right"] == "gdelta":      # generalized delta rule; the halves' outputs are normed and averaged
+                lc.r_kind = _seqabi.DN_RIGHT_GDELTA
+                lc.rank = from_shape(f"l{i}.mix.right.w1", 0, r, "rank", f"layer {i}")
+                lc.branch_norm = int(fam["branch_norm"])
+                lc.left_scale = lc.right_scale = float(fam.get("branch_scale", 1.0))
+            else:
+                lc.tau = float(r["tau"])
+                lc.rank = from_shape(f"l{i}.mix.right.a1", 0, r, "rank", f"layer {i}")
+                lc.left_scale, lc.right_scale = float(mx.get("left_scale", 1.0)), float(mx.get("right_scale", 1.0))
         elif kind == "wkv":
             lc.mixer = _seqabi.DN_MIX_WKV
             lc.heads = lc.kv_heads = int(mx["heads"])
@@ -189,7 +223,12 @@ def parse_layer_list(cfg: dict, family: Optional[dict] = None,
     sc = _seqabi.SeqCfg(width=int(cfg["width"]), vocab=int(cfg["vocab"]), n_layers=len(layers), streams=int(cfg.get("streams", 0) or 0),
                         eps=float((cfg.get("norm") or {}).get("eps", 1e-6)),
                         embed_scale=float((cfg.get("embedding") or {}).get("scale", 1.0)))
-    sc.norm_kind = _seqabi.DN_NORM_DYT if fam["norm"] == "dyt" else _seqabi.DN_NORM_RMS
+    sc.norm_kind = {"dyt": _seqabi.DN_NORM_DYT, "layer": _seqabi.DN_NORM_LAYER}.get(fam["norm"], _seqabi.DN_NORM_RMS)
+    sc.canon_taps = int((cfg.get("canon") or {}).get("taps", 0) or 0)
+    bg = (cfg.get("embedding") or {}).get("bigram")
+    if bg:
+        sc.bigram_buckets, sc.bigram_mul_prev, sc.bigram_mul_cur = int(bg["buckets"]), int(bg["mul_prev"]), int(bg["mul_cur"])
+    sc.logit_scale = float(cfg.get("logit_scale", 1.0))
     sc.post_norm, sc.embed_norm, sc.no_pre_norm = int(fam["post_norm"]), int(fam["embed_norm"]), int(not fam["pre_norm"])
     sc.logit_softcap = float(cfg.get("logit_softcap", 0.0) or 0.0)
     lp = cfg.get("loop")
@@ -251,7 +290,10 @@ class SeqMixRingModel(BaseRingModel):
         W, V, S = self.hidden_size, self.vocab_size, int(self._cfg_struct.streams)
         sc = self._cfg_struct
         dyt = sc.norm_kind == _seqabi.DN_NORM_DYT
+        lnorm = sc.norm_kind == _seqabi.DN_NORM_LAYER
         out: Dict[str, Tuple[int, ...]] = {"embed": (V, W), "final.norm": (W,)}
+        if sc.bigram_buckets > 0:
+            out["bigram"] = (sc.bigram_buckets + 1, W)
         if not self.family.get("tied_head"):
             out["head"] = (V, W)
 
@@ -259,6 +301,8 @@ class SeqMixRingModel(BaseRingModel):
             out[name] = (W,)
             if dyt:
                 out[name + ".b"], out[name + ".alpha"] = (W,), ()
+            if lnorm:
+                out[name + ".b"] = (W,)
 
         norm("final.norm")
         if sc.embed_norm:
@@ -275,12 +319,18 @@ class SeqMixRingModel(BaseRingModel):
             own = not (att and lc.kv_from >= 0) and not latent
             if not sc.no_pre_norm:
                 norm(p + "norm1")
+            if sc.canon_taps > 0:
+                out[p + "canon1"] = (W, sc.canon_taps)
+                if lc.ff > 0:
+                    out[p + "canon2"] = (W, sc.canon_taps)
             if sc.post_norm:
                 norm(p + "post1")
             out[p + "mix.q"] = (cq, W)
             out[p + "mix.o"] = (W, co)
             if own:
                 out[p + "mix.k"], out[p + "mix.v"] = (ck, W), (cv, W)
+                if att and lc.v_is_k:
+                    del out[p + "mix.v"]
             if latent:
                 cq = lc.heads * (lc.dim + lc.rot_part)
                 out[p + "mix.q"] = (cq, lc.q_rank if lc.q_rank > 0 else W)
@@ -295,15 +345,24 @@ class SeqMixRingModel(BaseRingModel):
                 if own:
                     out[p + "mix.k.conv"], out[p + "mix.v.conv"] = (ck, lc.conv), (cv, lc.conv)
             if att:
-                if lc.qk_norm:
-                    out[p + "mix.q.norm"] = (cq,)
+                if lc.qk_norm:      # over the whole projection, or per head with one weight for all heads
+                    per_head = lc.qk_norm == _seqabi.DN_QKNORM_HEAD
+                    out[p + "mix.q.norm"] = (lc.dim,) if per_head else (cq,)
                     if own:
-                        out[p + "mix.k.norm"] = (ck,)
+                        out[p + "mix.k.norm"] = (lc.dim,) if per_head else (ck,)
                 if lc.sink:
                     out[p + "sink"] = (lc.heads,)
                 if lc.out_gate:
                     out[p + "head_gate"] = (lc.heads, W)
-            if lc.mixer == _seqabi.DN_MIX_PARALLEL:
+            if lc.mixer == _seqabi.DN_MIX_PARALLEL and lc.r_kind == _seqabi.DN_RIGHT_GDELTA:
+                rc = lc.r_heads * lc.r_dim
+                for q in "qkvga":
+                    out[p + "r." + q] = (rc, W)
+                out[p + "r.ab"] = out[p + "r.norm"] = out[p + "decay.b"] = (rc,)
+                out[p + "decay1"], out[p + "decay2"], out[p + "r.o"] = (lc.rank, W), (rc, lc.rank), (W, rc)
+                if lc.branch_norm:
+                    out[p + "l.out"] = out[p + "r.out"] = (W,)
+            elif lc.mixer == _seqabi.DN_MIX_PARALLEL:
                 rc, rv = lc.r_heads * lc.r_dim, lc.r_heads * lc.r_vdim
                 out[p + "r.q"] = out[p + "r.k"] = (rc, W)
                 out[p + "r.v"] = out[p + "r.g"] = (rv, W)
@@ -532,4 +591,25 @@ class LutesunRingModel(SeqMixRingModel):
     tensor_alias = {
         "*": {"norm1": "post1", "norm2": "post2", **_MOE_ALIAS, "mlp.correction": "router.corr", "mlp.shared.sg": "shared.sg"},
         "latent_attention_2": {"mix.uq": "mix.q", "mix.g": "head_gate"},
+    }
+
+
+class VulanexRingModel(SeqMixRingModel):
+    """Vulanex: layer norms with bias before every sublayer, whose input then passes a short causal convolution over time
+    (its last inputs carried per sequence); the embedding adds a row of a hashed (previous token, token) table; layers are
+    either GQA attention whose values are its keys, without positions but with a query scale that grows with the logarithm
+    of the position, or a parallel mixer -- attention with per-head q / k norms, interpolated rotary frequencies, a
+    sliding window behind which blocks of tokens are seen as one mean key / value each, and a sink, beside a generalized
+    delta rule with a decay and a removal rate per key channel -- whose two outputs are RMS-normed and averaged; a dense
+    gelu-gated feed-forward; the embedding table is the output head and the logits are scaled."""
+
+    model_type = "vulanex"
+    family = {"norm": "layer", "tied_head": True, "mask": "window", "rot_layout": "half", "right": "gdelta", "branch_norm": True,
+              "branch_scale": 0.5, "qk_norm": {"parallel": "head"}, "sink": {"parallel": True}, "v_is_k": {"attention": True}}
+    tensor_alias = {
+        "parallel": {"mix.left.q": "mix.q", "mix.left.k": "mix.k", "mix.left.v": "mix.v", "mix.left.o": "mix.o", "mix.left.q.norm": "mix.q.norm",
+                     "mix.left.k.norm": "mix.k.norm", "mix.left.sink": "sink", "mix.left.out": "l.out", "mix.right.out": "r.out",
+                     "mix.right.r": "r.q", "mix.right.k": "r.k", "mix.right.v": "r.v", "mix.right.g": "r.g", "mix.right.a": "r.a",
+                     "mix.right.a.b": "r.ab", "mix.right.w1": "decay1", "mix.right.w2": "decay2", "mix.right.w0": "decay.b",
+                     "mix.right.norm": "r.norm", "mix.right.o": "r.o"},
     }

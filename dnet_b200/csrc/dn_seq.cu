@@ -5,6 +5,7 @@
 #include "dn_seq_recur.cuh"
 #include "dn_seq_moe.cuh"
 #include "dn_seq_latent.cuh"
+#include "dn_seq_gdelta.cuh"
 #include "dn_gemm_tc.cuh"      // the tcgen05 / TMA GEMM the llama-family prefill runs on (namespace dn)
 #include "../../include/dnet_b200_seq.h"
 
@@ -78,6 +79,7 @@ struct Run {
   bool inject;                  // a pass of the loop starts here: x <- W_in [x; x0] first
   int kv_index;                 // attention: which page pool (own or the one it borrows); -1 without attention
   size_t conv_off, state_off;   // element offsets into a slot's carried inputs (conv taps, shifted row) / fp32 state
+  size_t canon_off[2];          // ... and of the carried rows of the two sublayers' input convolutions
 };
 
 struct dn_seq_model {
@@ -103,6 +105,10 @@ struct dn_seq_model {
   int max_tiles = 0;
   // state
   std::vector<void*> kpool, vpool;
+  std::vector<void*> pkpool, pvpool;     // mean-pooled blocks behind a sliding window: [pages][pool_rows][row] (null: the run has none)
+  std::vector<int> last_tok;             // per slot: the sequence's last token (-1: none yet), for the bigram row
+  void* hn = nullptr;                    // the normed rows before the sublayer's input convolution [MB, W]
+  float *un = nullptr, *aun = nullptr;   // generalized delta rule: unit keys, removal rate times unit key [MB, C]
   void* conv_state = nullptr;
   size_t conv_stride = 0;       // elements per slot
   float* delta_state = nullptr;
@@ -197,7 +203,7 @@ extern "C" int dn_seq_model_destroy(dn_seq_model* m) {
   cudaDeviceSynchronize();
   void* ptrs[] = {m->xs, m->y, m->pa, m->pb, m->qn, m->kn, m->vv, m->od, m->beta, m->decay, m->h, m->uq, m->uk, m->uv, m->qb,
                   m->mo, m->gt, m->act, m->conv_state, m->delta_state, m->stage_d, m->bt_d, m->tc_err, m->y2, m->x0, m->dz, m->rwt,
-                  m->eo, m->cat, m->xm, m->lr, m->eact, m->ridx, m->rpos, m->rtok, m->tiles, m->xg, m->attn_part, m->sgate};
+                  m->eo, m->cat, m->xm, m->lr, m->eact, m->ridx, m->rpos, m->rtok, m->tiles, m->xg, m->attn_part, m->sgate, m->hn, m->un, m->aun};
   for (void* p : ptrs) if (p) cudaFree(p);
   for (auto& g : m->graphs) cudaGraphExecDestroy(g.second.first);
   if (m->lg_buf) cudaFree(m->lg_buf);
@@ -205,6 +211,8 @@ extern "C" int dn_seq_model_destroy(dn_seq_model* m) {
   for (cudaEvent_t ev : m->prof_pool) cudaEventDestroy(ev);
   for (void* p : m->kpool) if (p) cudaFree(p);
   for (void* p : m->vpool) if (p) cudaFree(p);
+  for (void* p : m->pkpool) if (p) cudaFree(p);
+  for (void* p : m->pvpool) if (p) cudaFree(p);
   for (auto& l : m->L) { if (l.inv_freq) cudaFree(l.inv_freq); if (l.etab_d) cudaFree((void*)l.etab_d); if (l.emaps_d) cudaFree(l.emaps_d); }
   if (m->stage_h) cudaFreeHost(m->stage_h);
   if (m->bt_h) cudaFreeHost(m->bt_h);
@@ -229,13 +237,18 @@ extern "C" int dn_seq_model_create(const dn_seq_cfg* cfg, const dn_seq_layer_cfg
   m->max_pages = cfg->pool_pages;
   m->L.resize(cfg->n_layers);
   int mq = 1, mk = 1, mv = 1, mo = 1, mh = 1, mff = 1, mdq = 1, mrank = 1, mpairs = 0, meff = 1, mexp = 1;
-  bool any_wkv = false;
+  bool any_wkv = false, any_gdelta = false;
   int rc = DN_OK;
   const bool looped = cfg->loop_times > 0;
   if (looped && (cfg->loop_start < 0 || cfg->loop_stop > cfg->n_layers || cfg->loop_start >= cfg->loop_stop))
     rc = fail(DN_EINVAL, "loop [%d, %d) x %d does not fit %d layers", cfg->loop_start, cfg->loop_stop, cfg->loop_times, cfg->n_layers);
-  if (rc == DN_OK && cfg->norm_kind != DN_NORM_RMS && cfg->norm_kind != DN_NORM_DYT) rc = fail(DN_EINVAL, "norm kind %d unknown", cfg->norm_kind);
-  if (rc == DN_OK && cfg->norm_kind == DN_NORM_RMS && cfg->embed_norm) rc = fail(DN_EINVAL, "a norm on the embedding exists as dynamic tanh only");
+  if (rc == DN_OK && cfg->norm_kind != DN_NORM_RMS && cfg->norm_kind != DN_NORM_DYT && cfg->norm_kind != DN_NORM_LAYER) rc = fail(DN_EINVAL, "norm kind %d unknown", cfg->norm_kind);
+  if (rc == DN_OK && cfg->norm_kind != DN_NORM_DYT && cfg->embed_norm) rc = fail(DN_EINVAL, "a norm on the embedding exists as dynamic tanh only");
+  if (rc == DN_OK && cfg->norm_kind == DN_NORM_LAYER && (cfg->post_norm || cfg->no_pre_norm)) rc = fail(DN_EINVAL, "layer norms stand before the sublayers only");
+  if (rc == DN_OK && (cfg->canon_taps < 0 || cfg->canon_taps > 9 || (cfg->canon_taps > 0 && (cfg->no_pre_norm || cfg->norm_kind == DN_NORM_DYT || cfg->loop_times > 0))))
+    rc = fail(DN_EINVAL, "input convolutions of %d taps unsupported (0..9, behind an RMS or layer norm before the sublayer, no loop)", cfg->canon_taps);
+  if (rc == DN_OK && (cfg->bigram_buckets < 0 || (cfg->bigram_buckets > 0 && (cfg->bigram_mul_prev < 0 || cfg->bigram_mul_cur < 0))))
+    rc = fail(DN_EINVAL, "bigram table of %d buckets with multipliers %d / %d unsupported", cfg->bigram_buckets, cfg->bigram_mul_prev, cfg->bigram_mul_cur);
   if (rc == DN_OK && cfg->norm_kind == DN_NORM_RMS && cfg->post_norm && cfg->streams > 0)
     rc = fail(DN_EINVAL, "an RMS norm after a sublayer joins the plain residual only (streams = 0)");
   for (int i = 0; i < cfg->n_layers && rc == DN_OK; i++) {
@@ -270,13 +283,54 @@ extern "C" int dn_seq_model_create(const dn_seq_cfg* cfg, const dn_seq_layer_cfg
         l.Ck = c.kv_heads * c.dim;
         l.Cv = c.kv_heads * c.vdim;
       }
+      if (c.v_is_k) {
+        if (c.vdim != c.dim || c.kv_from >= 0 || c.conv > 0) { rc = fail(DN_EINVAL, "layer %d: values that are the keys need vdim = dim, own keys and no convolutions", i); break; }
+        l.Cv = 0;      // one pool: the value of a token is its key row
+      }
+      if (c.qk_norm < DN_QKNORM_NONE || c.qk_norm > DN_QKNORM_HEAD) { rc = fail(DN_EINVAL, "layer %d: q / k norm %d unknown", i, c.qk_norm); break; }
+      if (c.pool < 0 || (c.pool > 0 && (c.mask_kind != DN_MASK_WINDOW || c.chunk <= 0 || c.kv_from >= 0))) {
+        rc = fail(DN_EINVAL, "layer %d: pooled blocks of %d tokens stand behind a sliding window of the layer's own keys", i, c.pool);
+        break;
+      }
+      if (c.qtemp_every < 0 || (c.rot_layout == DN_ROT_HALF && c.dim < c.rot_dims)) { rc = fail(DN_EINVAL, "layer %d: query scale / rotary layout unsupported", i); break; }
       if (c.rot_dims > 0) {
+        // frequencies base^(-2j/dims); scaled: dims that turn fast within the original context keep theirs, slow ones are
+        // divided by the factor, a linear ramp over the dim index between
         std::vector<float> f(c.rot_dims / 2);
-        for (int j = 0; j < c.rot_dims / 2; j++) f[j] = (float)std::pow((double)c.rot_base, -2.0 * j / (double)c.rot_dims);
+        const double dims = c.rot_dims, base = c.rot_base;
+        double lo = 0, hi = 0;
+        if (c.yarn_factor > 0.f) {
+          auto dim_of = [&](double turns) { return dims * std::log((double)c.yarn_original / (2.0 * M_PI * turns)) / (2.0 * std::log(base)); };
+          lo = std::max(std::floor(dim_of(c.yarn_fast)), 0.0);
+          hi = std::min(std::ceil(dim_of(c.yarn_slow)), dims - 1.0);
+        }
+        for (int j = 0; j < c.rot_dims / 2; j++) {
+          double fj = std::pow(base, -2.0 * j / dims);
+          if (c.yarn_factor > 0.f) {
+            const double ramp = std::min(1.0, std::max(0.0, ((double)j - lo) / std::max(hi - lo, 0.001)));
+            fj = fj / (double)c.yarn_factor * ramp + fj * (1.0 - ramp);
+          }
+          f[j] = (float)fj;
+        }
         if ((rc = dalloc(&l.inv_freq, f.size() * 4)) != DN_OK) break;
         if (cudaMemcpy(l.inv_freq, f.data(), f.size() * 4, cudaMemcpyHostToDevice) != cudaSuccess) { rc = fail(DN_ECUDA, "inv_freq upload failed"); break; }
       }
-      if (c.mixer == DN_MIX_PARALLEL) {
+      if (c.mixer == DN_MIX_PARALLEL && c.branch_norm && (cfg->streams > 0 || cfg->post_norm)) {
+        rc = fail(DN_EINVAL, "layer %d: normed halves of a parallel mixer join the plain residual without a norm after the sublayer", i);
+        break;
+      }
+      if (c.mixer == DN_MIX_PARALLEL && c.r_kind == DN_RIGHT_GDELTA) {
+        if (c.r_heads <= 0 || c.r_dim <= 0 || c.r_dim > 1024 || c.r_vdim != c.r_dim || c.rank <= 0 || c.conv > 0 || c.kv_from >= 0) {
+          rc = fail(DN_EINVAL, "layer %d: generalized delta rule with heads %d / dim %d / vdim %d / rank %d unsupported", i, c.r_heads, c.r_dim, c.r_vdim, c.rank);
+          break;
+        }
+        l.Rc = l.Rv = c.r_heads * c.r_dim;
+        mdq = std::max(mdq, l.Rc);
+        mrank = std::max(mrank, c.rank);
+        mh = std::max(mh, c.r_heads);
+        any_gdelta = true;
+      } else if (c.mixer == DN_MIX_PARALLEL) {
+        if (c.r_kind != DN_RIGHT_GLA) { rc = fail(DN_EINVAL, "layer %d: right half %d unknown", i, c.r_kind); break; }
         if (c.r_heads <= 0 || c.r_dim <= 0 || c.r_dim > 1024 || c.r_vdim <= 0 || c.rank <= 0 || !(c.tau > 0.f)) {
           rc = fail(DN_EINVAL, "layer %d: linear-attention half heads %d / dim %d / vdim %d / rank %d / tau %g unsupported", i, c.r_heads, c.r_dim, c.r_vdim, c.rank, c.tau);
           break;
@@ -375,7 +429,7 @@ extern "C" int dn_seq_model_create(const dn_seq_cfg* cfg, const dn_seq_layer_cfg
     }
     std::vector<int> last_run(cfg->n_layers, -1);
     for (auto& o : order) {
-      Run r{o.first, o.second, -1, 0, 0};
+      Run r{o.first, o.second, -1, 0, 0, {0, 0}};
       const SeqLayer& l = m->L[r.layer];
       const dn_seq_layer_cfg& c = l.c;
       if (c.mixer == DN_MIX_ATTENTION || c.mixer == DN_MIX_PARALLEL || c.mixer == DN_MIX_LATENT) {
@@ -384,9 +438,20 @@ extern "C" int dn_seq_model_create(const dn_seq_cfg* cfg, const dn_seq_layer_cfg
           r.kv_index = (int)m->kpool.size();
           m->kpool.push_back(nullptr);
           m->vpool.push_back(nullptr);
+          m->pkpool.push_back(nullptr);
+          m->pvpool.push_back(nullptr);
           if ((rc = dalloc(&m->kpool.back(), (size_t)cfg->pool_pages * PAGE * l.Ck * m->esz)) != DN_OK) break;
           if ((rc = dalloc(&m->vpool.back(), (size_t)cfg->pool_pages * PAGE * l.Cv * m->esz)) != DN_OK) break;
+          if (c.pool > 0) {
+            const size_t rows = (size_t)cfg->pool_pages * pool_rows(c.pool);
+            if ((rc = dalloc(&m->pkpool.back(), rows * l.Ck * m->esz)) != DN_OK) break;
+            if ((rc = dalloc(&m->pvpool.back(), rows * l.Cv * m->esz)) != DN_OK) break;
+          }
         }
+      }
+      for (int q = 0; q < 2; q++) {
+        r.canon_off[q] = coff;
+        if (cfg->canon_taps > 1 && (q == 0 || c.ff > 0)) coff += (size_t)(cfg->canon_taps - 1) * cfg->width;
       }
       r.conv_off = coff;
       if (c.conv > 1) coff += (size_t)(c.conv - 1) * (l.Cq + l.Ck + l.Cv);
@@ -410,6 +475,8 @@ extern "C" int dn_seq_model_create(const dn_seq_cfg* cfg, const dn_seq_layer_cfg
   DA(m->sgate, MB * 4);
   if (looped) { DA(m->x0, MB * W * 4); DA(m->cat, MB * 2 * W * e); }
   if (any_wkv) DA(m->xm, (size_t)SHIFT_MAX * MB * W * e);
+  if (cfg->canon_taps > 0) DA(m->hn, MB * W * e);
+  if (any_gdelta) { DA(m->un, MB * mdq * 4); DA(m->aun, MB * mdq * 4); }
   if (mpairs > 0) {
     const size_t P = MB * mpairs;
     m->max_tiles = (int)(P / MOE_ROWS) + mexp + 1;
@@ -420,7 +487,7 @@ extern "C" int dn_seq_model_create(const dn_seq_cfg* cfg, const dn_seq_layer_cfg
   DA(m->h, MB * W * e); DA(m->uq, MB * mq * e); DA(m->uk, MB * mk * e); DA(m->uv, MB * mv * e); DA(m->qb, MB * mq * e);
   DA(m->mo, MB * mo * e); DA(m->gt, MB * mo * e); DA(m->act, MB * mff * e);
   DA(m->conv_state, (size_t)cfg->max_seqs * coff * e); DA(m->delta_state, (size_t)cfg->max_seqs * doff * 4);
-  m->stage_ints = 4 * MB + 3 * (size_t)(cfg->max_seqs + 1) + MB;
+  m->stage_ints = 5 * MB + 3 * (size_t)(cfg->max_seqs + 1) + MB;
   DA(m->stage_d, m->stage_ints * 4); DA(m->bt_d, (size_t)cfg->max_seqs * m->max_pages * 4); DA(m->tc_err, 16);
   DA(m->lg_buf, (size_t)8 * cfg->vocab * 4);
 #undef DA
@@ -452,6 +519,7 @@ extern "C" int dn_seq_model_create(const dn_seq_cfg* cfg, const dn_seq_layer_cfg
   for (int s = cfg->max_seqs - 1; s >= 0; s--) m->free_slots.push_back(s);
   m->pages.resize(cfg->max_seqs);
   m->length.assign(cfg->max_seqs, -1);
+  m->last_tok.assign(cfg->max_seqs, -1);
   *out = m;
   return DN_OK;
 }
@@ -467,7 +535,7 @@ extern "C" int dn_seq_bind(dn_seq_model* m, int layer, int which, const void* p)
     else if (which == DN_SQ_HEAD) {
       m->head = p;
       m->tm_head_ok = b16 && make_tmap(&m->tm_head, p, m->cfg.vocab, m->cfg.width, dn::TC_BM);
-    } else if (which > DN_SQ_HEAD && which <= DN_SQ_LOOP_IN) {
+    } else if (which > DN_SQ_HEAD && which <= DN_SQ_BIGRAM) {
       m->mw[which - DN_SQ_EMBED] = p;
       if (which == DN_SQ_LOOP_IN) m->tm_loop_ok = b16 && make_tmap(&m->tm_loop_in, p, m->cfg.width, 2 * m->cfg.width, dn::TC_BM);
     } else return fail(DN_EINVAL, "tensor %d is not a model tensor", which);
@@ -489,7 +557,7 @@ extern "C" int dn_seq_bind(dn_seq_model* m, int layer, int which, const void* p)
     case DN_SQ_O: rows = m->cfg.width; cols = l.Co; break;
     case DN_SQ_DOWN: rows = m->cfg.width; cols = l.c.ff; break;
     case DN_SQ_HEAD_GATE: rows = l.c.heads; break;
-    case DN_SQ_R_Q: case DN_SQ_R_K: rows = l.Rc; break;
+    case DN_SQ_R_Q: case DN_SQ_R_K: case DN_SQ_R_A: rows = l.Rc; break;
     case DN_SQ_R_V: case DN_SQ_R_G: rows = l.Rv; break;
     case DN_SQ_R_O: rows = m->cfg.width; cols = l.Rv; break;
     case DN_SQ_DECAY1: rows = l.c.rank; break;
@@ -534,6 +602,7 @@ extern "C" int dn_seq_open(dn_seq_model* m, dn_seq_stream s, int* slot_out) {
   if (m->delta_stride) CK(cudaMemsetAsync(m->delta_state + (size_t)slot * m->delta_stride, 0, m->delta_stride * 4, (cudaStream_t)s));
   m->free_slots.pop_back();
   m->length[slot] = 0;
+  m->last_tok[slot] = -1;
   m->pages[slot].clear();
   *slot_out = slot;
   return DN_OK;
@@ -852,6 +921,8 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
   const int ew = (int)((NW + 255) / 256), ew4 = (int)((NW / 4 + 255) / 256);
   const dim3 nthr(W >= 4096 ? 512 : W >= 2048 ? 256 : 128);     // threads of a norm block: a function of the width only
   const bool dyt = c.norm_kind == DN_NORM_DYT;
+  const int lnorm = c.norm_kind == DN_NORM_LAYER ? 1 : 0;
+  const int taps = c.canon_taps;
   const bool pre = !c.no_pre_norm;      // false: the sublayers read the residual itself, h = T(x)
   auto mwp = [&](int which) { return (const T*)m->mw[which - DN_SQ_EMBED]; };
   auto write_back = [&](const T* mix, const T* out) {
@@ -885,7 +956,27 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
 #define PH(id) CK(mark(m, id, s))
   PH(DN_SEQ_PH_EMBED);
   CK(launch(k_embed<T>, dim3(N), dim3(128), 0, s, (const T*)m->embed, b, c.embed_scale, W, S1, m->xs, mwp(DN_SQ_EMBED_NORM), mwp(DN_SQ_EMBED_NORM_B),
-            c.embed_norm ? mwp(DN_SQ_EMBED_NORM_ALPHA) : (const T*)nullptr, m->x0, pre ? (T*)nullptr : (T*)m->h));
+            c.embed_norm ? mwp(DN_SQ_EMBED_NORM_ALPHA) : (const T*)nullptr, m->x0, pre ? (T*)nullptr : (T*)m->h,
+            c.bigram_buckets > 0 ? mwp(DN_SQ_BIGRAM) : (const T*)nullptr));
+  // the norm before a sublayer and, where the model has them, the sublayer's input convolution with its carried rows
+  auto norm_in = [&](SeqLayer& l, const Run& run, int q) -> int {
+    auto w = [&](int i) { return (const T*)l.w[i]; };
+    const int nrm = q == 0 ? DN_SQ_NORM1 : DN_SQ_NORM2, nb = q == 0 ? DN_SQ_NORM1_B : DN_SQ_NORM2_B, na = q == 0 ? DN_SQ_NORM1_ALPHA : DN_SQ_NORM2_ALPHA;
+    T* dst = taps > 0 ? (T*)m->hn : (T*)m->h;
+    CK(launch(k_read_norm<T>, dim3(N), nthr, nsm, s, m->xs, N, W, S, w(q == 0 ? DN_SQ_HC1_IN : DN_SQ_HC2_IN), w(nrm), dyt ? 0 : 1, 0, c.eps, (const int32_t*)nullptr, dst,
+              w(nb), dyt ? w(na) : (const T*)nullptr, lnorm));
+    if (taps > 0) {
+      CK(mark(m, DN_SEQ_PH_CANON, s));
+      T* cst = (T*)m->conv_state + run.canon_off[q];
+      const int fused = b.max_len == 1 ? 1 : 0;      // every entry one token: the kernel carries the row itself
+      CK(launch(k_canon<T>, dim3(N), dim3(W >= 1024 ? 256 : 128), 0, s, (const T*)m->hn, w(q == 0 ? DN_SQ_CANON1 : DN_SQ_CANON2), taps, b, W, cst, m->conv_stride, (T*)m->h, fused));
+      if (!fused && taps > 1) {
+        CarrySrc<T> cs{{(const T*)m->hn, nullptr, nullptr}, {W, 0, 0}};
+        CK(launch(k_conv_carry<T>, dim3((W + 127) / 128, b.E, 1), dim3(128), 0, s, cs, taps, b, cst, m->conv_stride));
+      }
+    }
+    return DN_OK;
+  };
   bool h_ready = !pre;
   for (int ri = 0; ri < (int)m->runs.size(); ri++) {
     const Run& run = m->runs[ri];
@@ -903,9 +994,10 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
     PH(DN_SEQ_PH_NORM);
     if (!pre) {
       if (!h_ready || run.inject) CK(launch(k_cast<T>, dim3(ew), dim3(256), 0, s, (const float*)m->xs, NW, (T*)m->h));
-    } else if (!h_ready || run.inject)
-      CK(launch(k_read_norm<T>, dim3(N), nthr, nsm, s, m->xs, N, W, S, w(DN_SQ_HC1_IN), w(DN_SQ_NORM1), dyt ? 0 : 1, 0, c.eps, (const int32_t*)nullptr, (T*)m->h,
-                w(DN_SQ_NORM1_B), dyt ? w(DN_SQ_NORM1_ALPHA) : (const T*)nullptr));
+    } else if (!h_ready || run.inject) {
+      const int rc = norm_in(l, run, 0);
+      if (rc != DN_OK) return rc;
+    }
     h_ready = false;
     // what the join after this run's last sublayer can prepare: the next run's first norm, unless a loop pass starts there
     const bool next_ok = can_fuse_next && ri + 1 < (int)m->runs.size() && !m->runs[ri + 1].inject;
@@ -942,22 +1034,33 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
       }
     }
     if (lc.mixer == DN_MIX_ATTENTION || lc.mixer == DN_MIX_PARALLEL) {
-      AttnPrep a{lc.heads, lc.kv_heads, lc.dim, lc.vdim, lc.conv, lc.rot_dims, l.Ck ? 1 : 0, lc.qk_norm, c.eps, l.inv_freq};
-      AttnExtra ex{lc.softcap, lc.sink ? l.w[DN_SQ_SINK] : nullptr, lc.out_gate ? (const float*)m->pa : nullptr, lc.mask_kind == DN_MASK_WINDOW ? 1 : 0, 0};
-      const size_t sm = ((size_t)l.Cq + l.Ck + 40) * 4;
+      AttnPrep a{lc.heads, lc.kv_heads, lc.dim, lc.vdim, lc.conv, lc.rot_dims, l.Ck ? 1 : 0, lc.qk_norm, c.eps, l.inv_freq,
+                 lc.v_is_k ? 0 : 1, lc.rot_layout == DN_ROT_HALF ? 1 : 0, lc.yarn_factor > 0.f ? 0.1f * logf(lc.yarn_factor) + 1.f : 1.f,
+                 lc.qtemp_coef, lc.qtemp_every};
+      // values that are the keys: the value pool is the key pool (row stride G dk); the pooled rows likewise
+      const void* vpl = lc.v_is_k ? m->kpool[run.kv_index] : m->vpool[run.kv_index];
+      void* pkp = m->pkpool[run.kv_index];
+      void* pvp = lc.v_is_k ? pkp : m->pvpool[run.kv_index];
+      const int Ckk = lc.kv_heads * lc.dim;
+      AttnExtra ex{lc.softcap, lc.sink ? l.w[DN_SQ_SINK] : nullptr, lc.out_gate ? (const float*)m->pa : nullptr, lc.mask_kind == DN_MASK_WINDOW ? 1 : 0,
+                   lc.v_is_k ? Ckk : 0, lc.pool, pkp, pvp};
+      const size_t sm = ((size_t)l.Cq + l.Ck + 40 + lc.heads + lc.kv_heads + lc.rot_dims) * 4;
       PH(DN_SEQ_PH_ATTN_PREP);
       CK(launch(k_attn_prep<T>, dim3(N), dim3(256), sm, s, a, b, (const T*)m->uq, (const T*)m->uk, (const T*)m->uv, w(DN_SQ_Q_CONV),
                 w(DN_SQ_K_CONV), w(DN_SQ_V_CONV), w(DN_SQ_Q_NORM), w(DN_SQ_K_NORM), (const T*)cst, m->conv_stride, (T*)m->qb,
                 (T*)m->kpool[run.kv_index], (T*)m->vpool[run.kv_index]));
+      if (lc.pool > 0)      // blocks that this step's tokens complete get their mean key and value
+        CK(launch(k_pool_rows<T>, dim3(N), dim3(128), 0, s, b, lc.pool, Ckk, lc.v_is_k ? 0 : lc.kv_heads * lc.vdim, (const T*)m->kpool[run.kv_index], (const T*)vpl,
+                  (T*)pkp, (T*)pvp));
       PH(DN_SEQ_PH_ATTN);
       if (attn_tiles_ok<T>(lc, b))
-        CK(attn_tiles(s, b, (const bf16*)m->qb, (const bf16*)m->kpool[run.kv_index], (const bf16*)m->vpool[run.kv_index], lc, ex, (bf16*)m->mo));
+        CK(attn_tiles(s, b, (const bf16*)m->qb, (const bf16*)m->kpool[run.kv_index], (const bf16*)vpl, lc, ex, (bf16*)m->mo));
       else {
         // a small step (decode): long rows are split over up to AT_MAX_SPLITS blocks, joined by k_attn_merge
         const int Z = N <= AT_SPLIT_ROWS ? AT_MAX_SPLITS : 1;
         CK(launch(k_attn<T, 8>, dim3(N, lc.heads, Z), dim3(AT_WARPS * 32), (size_t)(((lc.dim + 3) & ~3) + AT_WARPS * (2 + (lc.vdim + 31) / 32 * 32)) * 4, s, b,
                   (const T*)m->qb, (const T*)m->kpool[run.kv_index],
-                  (const T*)m->vpool[run.kv_index], lc.heads, lc.kv_heads, lc.dim, lc.vdim, lc.chunk, lc.scale, ex, (T*)m->mo, m->attn_part));
+                  (const T*)vpl, lc.heads, lc.kv_heads, lc.dim, lc.vdim, lc.chunk, lc.scale, ex, (T*)m->mo, m->attn_part));
         if (Z > 1) CK(launch(k_attn_merge<T>, dim3(N, lc.heads), dim3(128), 0, s, b, lc.heads, lc.vdim, lc.chunk, Z, ex, (const float*)m->attn_part, (T*)m->mo));
       }
     } else if (lc.mixer == DN_MIX_LATENT) {
@@ -1047,7 +1150,7 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
 #undef DR
       PH(DN_SEQ_PH_DELTA_OUT);
       CK(launch(k_delta_out<T>, dim3(N, lc.heads), dim3(32), 0, s, (const float*)m->od, (const T*)m->gt, w(DN_SQ_OUT_NORM), lc.heads, lc.vdim,
-                c.eps, (T*)m->mo, 0));
+                c.eps, (T*)m->mo, 0, 0));
     } else {     // DN_MIX_WKV: token-shifted inputs, projections of each, the recurrence read with a bonus
       PH(DN_SEQ_PH_PROJ);
       ShiftMu<T> mu{{w(DN_SQ_MU_R), w(DN_SQ_MU_K), w(DN_SQ_MU_V), w(DN_SQ_MU_G), w(DN_SQ_MU_W)}, 5};
@@ -1077,7 +1180,7 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
       { const int rc = decay_rule(m, b, RECUR_BONUS, lc.heads, lc.dim, lc.vdim, l.w[DN_SQ_BONUS], st, s); if (rc != DN_OK) return rc; }
       PH(DN_SEQ_PH_RECUR_OUT);
       CK(launch(k_delta_out<T>, dim3(N, lc.heads), dim3(32), 0, s, (const float*)m->od, (const T*)m->gt, w(DN_SQ_OUT_NORM), lc.heads, lc.vdim,
-                c.eps, (T*)m->mo, lc.vdim));
+                c.eps, (T*)m->mo, lc.vdim, 0));
     }
     if (lc.conv > 1) {
       PH(DN_SEQ_PH_CARRY);
@@ -1086,7 +1189,48 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
     }
     PH(DN_SEQ_PH_OUT_PROJ);
     CK(linear<T>(m, s, (const T*)m->mo, l.w[DN_SQ_O], nullptr, m->y, N, W, l.Co, true, 0, LinMaps{wm(DN_SQ_O), nullptr, &l.x_mo}));
-    if (lc.mixer == DN_MIX_PARALLEL) {     // the linear-attention half, on the same input; its scratch is free again
+    if (lc.mixer == DN_MIX_PARALLEL && lc.r_kind == DN_RIGHT_GDELTA) {     // the generalized delta rule, on the same input
+      PH(DN_SEQ_PH_PROJ);
+      if (few) {
+        memset(&sg, 0, sizeof(sg));
+        add(nullptr, DN_SQ_R_Q, m->uq, l.Rc, 0); add(nullptr, DN_SQ_R_K, m->uk, l.Rc, 0); add(nullptr, DN_SQ_R_V, m->uv, l.Rv, 0);
+        add(nullptr, DN_SQ_R_G, m->gt, l.Rv, 0); add(nullptr, DN_SQ_R_A, m->aun, l.Rc, 1); add(nullptr, DN_SQ_DECAY1, m->lr, lc.rank, 0);
+        sg.act[sg.n - 1] = ACT_TANH;
+        CK(run_segs());
+      } else {
+        CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_R_Q], nullptr, m->uq, N, l.Rc, W, false, 0, LinMaps{wm(DN_SQ_R_Q), nullptr, &m->x_h}));
+        CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_R_K], nullptr, m->uk, N, l.Rc, W, false, 0, LinMaps{wm(DN_SQ_R_K), nullptr, &m->x_h}));
+        CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_R_V], nullptr, m->uv, N, l.Rv, W, false, 0, LinMaps{wm(DN_SQ_R_V), nullptr, &m->x_h}));
+        CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_R_G], nullptr, m->gt, N, l.Rv, W, false, 0, LinMaps{wm(DN_SQ_R_G), nullptr, &m->x_h}));
+        CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_R_A], nullptr, m->aun, N, l.Rc, W, true, 0, LinMaps{wm(DN_SQ_R_A), nullptr, &m->x_h}));
+        CK(linear<T>(m, s, (const T*)m->h, l.w[DN_SQ_DECAY1], nullptr, m->lr, N, lc.rank, W, false, ACT_TANH, LinMaps{wm(DN_SQ_DECAY1), nullptr, &m->x_h}));
+      }
+      CK(linear<T>(m, s, (const T*)m->lr, l.w[DN_SQ_DECAY2], nullptr, m->dz, N, l.Rc, lc.rank, true, 0, LinMaps{wm(DN_SQ_DECAY2), nullptr, &l.x_lr}));
+      PH(DN_SEQ_PH_RECUR_PREP);
+      CK(launch(k_gdelta_prep<T>, dim3(N), dim3(32 * std::min(8, lc.r_heads)), 0, s, lc.r_heads, lc.r_dim, (const T*)m->uq, (const T*)m->uk, (const T*)m->uv,
+                w(DN_SQ_DECAY_B), w(DN_SQ_R_AB), m->qn, m->kn, m->vv, m->dz, m->un, m->aun));
+      PH(DN_SEQ_PH_RECUR);
+      {
+        int R, P;
+        recur_shape(lc.r_dim, &R, &P);
+        const int cols = P >= 2 ? 16 : 32, dv = lc.r_dim;
+        dim3 grid(b.E * lc.r_heads, (dv + cols - 1) / cols);
+        const int per = 5 * P * (R + 4) + cols;
+        const int TB = std::max(1, std::min(16, 5800 / per));      // two tiles within ~46 KB of shared memory
+        const size_t dsm = (size_t)2 * TB * per * 4;
+#define GD(Rv_, Pv_, Cv_) if (R == Rv_ && P == Pv_) CK(launch(k_gdelta_rule<Rv_, Pv_, Cv_>, grid, dim3(Cv_ * Pv_), dsm, s, b, lc.r_heads, lc.r_dim, dv, TB, \
+                           (const float*)m->qn, (const float*)m->kn, (const float*)m->vv, (const float*)m->dz, (const float*)m->un, (const float*)m->aun, st, \
+                           m->delta_stride, m->od))
+        GD(8, 1, 32); GD(8, 2, 16); GD(8, 4, 16); GD(8, 8, 16); GD(16, 8, 16); GD(16, 16, 16); GD(16, 32, 16); GD(32, 32, 16);
+#undef GD
+      }
+      PH(DN_SEQ_PH_RECUR_OUT);
+      CK(launch(k_delta_out<T>, dim3(N, lc.r_heads), dim3(32), 0, s, (const float*)m->od, (const T*)m->gt, w(DN_SQ_R_NORM), lc.r_heads, lc.r_dim,
+                c.eps, (T*)m->mo, lc.r_dim, 1));
+      PH(DN_SEQ_PH_OUT_PROJ);
+      CK(linear<T>(m, s, (const T*)m->mo, l.w[DN_SQ_R_O], nullptr, m->y2, N, W, l.Rv, true, 0, LinMaps{wm(DN_SQ_R_O), nullptr, &l.x_mo_r}));
+      ja = lc.left_scale; jb = lc.right_scale; jy2 = m->y2;
+    } else if (lc.mixer == DN_MIX_PARALLEL) {     // the linear-attention half, on the same input; its scratch is free again
       PH(DN_SEQ_PH_PROJ);
       if (few) {
         memset(&sg, 0, sizeof(sg));
@@ -1108,21 +1252,25 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
       { const int rc = decay_rule(m, b, RECUR_AFTER, lc.r_heads, lc.r_dim, lc.r_vdim, nullptr, st, s); if (rc != DN_OK) return rc; }
       PH(DN_SEQ_PH_RECUR_OUT);
       CK(launch(k_delta_out<T>, dim3(N, lc.r_heads), dim3(32), 0, s, (const float*)m->od, (const T*)m->gt, w(DN_SQ_R_NORM), lc.r_heads, lc.r_vdim,
-                c.eps, (T*)m->mo, 0));
+                c.eps, (T*)m->mo, 0, 0));
       PH(DN_SEQ_PH_OUT_PROJ);
       CK(linear<T>(m, s, (const T*)m->mo, l.w[DN_SQ_R_O], nullptr, m->y2, N, W, l.Rv, true, 0, LinMaps{wm(DN_SQ_R_O), nullptr, &l.x_mo_r}));
       ja = lc.left_scale; jb = lc.right_scale; jy2 = m->y2;
     }
     PH(DN_SEQ_PH_WRITE_BACK);
     const NextNorm<T> nx_mix = lc.ff > 0 ? (can_fuse_next ? next_norm(l, DN_SQ_NORM2) : no_next) : nx_run;
-    CK(join(l, DN_SQ_POST1, DN_SQ_HC1_MIX, DN_SQ_HC1_OUT, ja, jy2, jb, nx_mix));
+    if (lc.mixer == DN_MIX_PARALLEL && lc.branch_norm)
+      CK(launch(k_rms2_join<T>, dim3(N), nthr, 0, s, m->xs, W, (const float*)m->y, ja, w(DN_SQ_L_OUT), jy2, jb, w(DN_SQ_R_OUT), c.eps));
+    else
+      CK(join(l, DN_SQ_POST1, DN_SQ_HC1_MIX, DN_SQ_HC1_OUT, ja, jy2, jb, nx_mix));
     if (lc.ff == 0) h_ready = nx_run.alpha != nullptr || !pre;
     // ---- feed-forward sublayer
     if (lc.ff > 0) {
       PH(DN_SEQ_PH_NORM);
-      if (!can_fuse_next && pre)
-        CK(launch(k_read_norm<T>, dim3(N), nthr, nsm, s, m->xs, N, W, S, w(DN_SQ_HC2_IN), w(DN_SQ_NORM2), dyt ? 0 : 1, 0, c.eps, (const int32_t*)nullptr, (T*)m->h,
-                  w(DN_SQ_NORM2_B), dyt ? w(DN_SQ_NORM2_ALPHA) : (const T*)nullptr));
+      if (!can_fuse_next && pre) {
+        const int rc = norm_in(l, run, 1);
+        if (rc != DN_OK) return rc;
+      }
       if (lc.mlp_kind == DN_MLP_MOE) {
         const bool fused = c.post_norm && S <= 0;
         const bool rmsj = fused && !dyt;      // the RMS join adds the pairs, the identity experts' input and the gated shared expert itself
@@ -1155,11 +1303,13 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
   if (n_want > 0) {
     PH(DN_SEQ_PH_NORM);
     CK(launch(k_read_norm<T>, dim3(n_want), nthr, nsm, s, m->xs, N, W, S, (const T*)nullptr, (const T*)m->final_norm, dyt ? 0 : 1, 1, c.eps, want_dev, (T*)m->h,
-              mwp(DN_SQ_FINAL_NORM_B), dyt ? mwp(DN_SQ_FINAL_NORM_ALPHA) : (const T*)nullptr));
+              mwp(DN_SQ_FINAL_NORM_B), dyt ? mwp(DN_SQ_FINAL_NORM_ALPHA) : (const T*)nullptr, lnorm));
     PH(DN_SEQ_PH_HEAD);
     CK(linear<T>(m, s, (const T*)m->h, m->head, nullptr, logits, n_want, c.vocab, W, true, 0, LinMaps{m->tm_head_ok ? &m->tm_head : nullptr, nullptr, &m->x_h}));
     if (c.logit_softcap > 0.f)
       CK(launch(k_softcap, dim3((unsigned)(((size_t)n_want * c.vocab + 255) / 256)), dim3(256), 0, s, logits, (size_t)n_want * c.vocab, c.logit_softcap));
+    if (c.logit_scale != 0.f && c.logit_scale != 1.f)
+      CK(launch(k_scale, dim3((unsigned)(((size_t)n_want * c.vocab + 255) / 256)), dim3(256), 0, s, logits, (size_t)n_want * c.vocab, c.logit_scale));
   }
   PH(DN_SEQ_PH_OTHER);
 #undef PH
@@ -1194,6 +1344,8 @@ extern "C" int dn_seq_step(dn_seq_model* m, int E, const int32_t* slots, const i
   if (dyt && (!mhas(DN_SQ_FINAL_NORM_B) || !mhas(DN_SQ_FINAL_NORM_ALPHA))) return fail(DN_ENOENT, "bias / alpha of the final norm are not bound");
   if (m->cfg.embed_norm && (!mhas(DN_SQ_EMBED_NORM) || !mhas(DN_SQ_EMBED_NORM_B) || !mhas(DN_SQ_EMBED_NORM_ALPHA))) return fail(DN_ENOENT, "the embedding's norm is not bound");
   if (m->cfg.loop_times > 0 && !mhas(DN_SQ_LOOP_IN)) return fail(DN_ENOENT, "the loop's input matrix is not bound");
+  if (m->cfg.norm_kind == DN_NORM_LAYER && !mhas(DN_SQ_FINAL_NORM_B)) return fail(DN_ENOENT, "the final norm's bias is not bound");
+  if (m->cfg.bigram_buckets > 0 && !mhas(DN_SQ_BIGRAM)) return fail(DN_ENOENT, "the bigram table is not bound");
   for (int i = 0; i < m->cfg.n_layers; i++) {
     const SeqLayer& l = m->L[i];
     auto has = [&](int k) { return l.w[k] != nullptr; };
@@ -1212,7 +1364,9 @@ extern "C" int dn_seq_step(dn_seq_model* m, int E, const int32_t* slots, const i
     if (m->cfg.post_norm && dyt) ok = ok && has(DN_SQ_POST1_B) && has(DN_SQ_POST1_ALPHA) && (l.c.ff == 0 || (has(DN_SQ_POST2_B) && has(DN_SQ_POST2_ALPHA)));
     if (mx == DN_MIX_LATENT) ok = ok && has(DN_SQ_DKV) && has(DN_SQ_DKV_NORM) && has(DN_SQ_UK) && has(DN_SQ_UV) && (!l.c.out_gate || has(DN_SQ_HEAD_GATE)) &&
                                   (l.c.q_rank == 0 || (has(DN_SQ_DQ) && has(DN_SQ_DQ_NORM)));
-    else if (l.Ck) ok = ok && has(DN_SQ_K) && has(DN_SQ_V);
+    else if (l.Ck) ok = ok && has(DN_SQ_K) && (l.c.v_is_k || has(DN_SQ_V));
+    if (m->cfg.norm_kind == DN_NORM_LAYER) ok = ok && has(DN_SQ_NORM1_B) && (l.c.ff == 0 || has(DN_SQ_NORM2_B));
+    if (m->cfg.canon_taps > 0) ok = ok && has(DN_SQ_CANON1) && (l.c.ff == 0 || has(DN_SQ_CANON2));
     if (l.c.conv > 0) ok = ok && has(DN_SQ_Q_CONV) && (!l.Ck || (has(DN_SQ_K_CONV) && has(DN_SQ_V_CONV)));
     if (mx == DN_MIX_ATTENTION || mx == DN_MIX_PARALLEL) {
       if (l.c.qk_norm) ok = ok && has(DN_SQ_Q_NORM) && (!l.Ck || has(DN_SQ_K_NORM));
@@ -1222,6 +1376,8 @@ extern "C" int dn_seq_step(dn_seq_model* m, int E, const int32_t* slots, const i
     if (mx == DN_MIX_DELTA) ok = ok && has(DN_SQ_A) && has(DN_SQ_B) && has(DN_SQ_G) && has(DN_SQ_A_LOG) && has(DN_SQ_DT_BIAS) && has(DN_SQ_OUT_NORM);
     if (mx == DN_MIX_PARALLEL) ok = ok && has(DN_SQ_R_Q) && has(DN_SQ_R_K) && has(DN_SQ_R_V) && has(DN_SQ_R_G) && has(DN_SQ_R_O) && has(DN_SQ_R_NORM) &&
                                     has(DN_SQ_DECAY1) && has(DN_SQ_DECAY2) && has(DN_SQ_DECAY_B);
+    if (mx == DN_MIX_PARALLEL && l.c.r_kind == DN_RIGHT_GDELTA) ok = ok && has(DN_SQ_R_A) && has(DN_SQ_R_AB);
+    if (mx == DN_MIX_PARALLEL && l.c.branch_norm) ok = ok && has(DN_SQ_L_OUT) && has(DN_SQ_R_OUT);
     if (mx == DN_MIX_WKV) ok = ok && has(DN_SQ_G) && has(DN_SQ_OUT_NORM) && has(DN_SQ_DECAY1) && has(DN_SQ_DECAY2) && has(DN_SQ_DECAY_B) && has(DN_SQ_BONUS) &&
                                has(DN_SQ_MU_R) && has(DN_SQ_MU_K) && has(DN_SQ_MU_V) && has(DN_SQ_MU_G) && has(DN_SQ_MU_W);
     if (m->cfg.streams > 0) ok = ok && has(DN_SQ_HC1_IN) && has(DN_SQ_HC1_OUT) && has(DN_SQ_HC1_MIX) &&
@@ -1231,7 +1387,8 @@ extern "C" int dn_seq_step(dn_seq_model* m, int E, const int32_t* slots, const i
   // the previous step's staging copies must have read the pinned buffers before they are rewritten
   CK(cudaEventSynchronize(m->staged));
   int32_t* h = m->stage_h;
-  int32_t *tok = h, *slot = h + N, *pos = h + 2 * N, *first = h + 3 * N, *es = h + 4 * N, *esl = es + E + 1, *ep0 = esl + E, *wr = ep0 + E;
+  int32_t *tok = h, *slot = h + N, *pos = h + 2 * N, *first = h + 3 * N, *brow = h + 4 * N, *es = h + 5 * N, *esl = es + E + 1, *ep0 = esl + E, *wr = ep0 + E;
+  const dn_seq_cfg& mc = m->cfg;
   int n = 0;
   for (int e = 0; e < E; e++) {
     const int sl = slots[e];
@@ -1247,19 +1404,26 @@ extern "C" int dn_seq_step(dn_seq_model* m, int E, const int32_t* slots, const i
       CK(cudaMemcpyAsync(m->bt_d + (size_t)sl * m->max_pages + had, m->bt_h + (size_t)sl * m->max_pages + had, (pages - had) * 4,
                          cudaMemcpyHostToDevice, s));
     es[e] = n; esl[e] = sl; ep0[e] = m->length[sl];
-    for (int i = 0; i < counts[e]; i++, n++) { tok[n] = tokens[n]; slot[n] = sl; pos[n] = m->length[sl] + i; first[n] = es[e]; }
+    for (int i = 0; i < counts[e]; i++, n++) {
+      tok[n] = tokens[n]; slot[n] = sl; pos[n] = m->length[sl] + i; first[n] = es[e];
+      // the bigram row: a hash of (previous token, token); the table's last row for a sequence's first token
+      const int prev = m->last_tok[sl];
+      brow[n] = mc.bigram_buckets <= 0 ? 0 : prev < 0 ? mc.bigram_buckets
+              : (int32_t)(((int64_t)prev * mc.bigram_mul_prev + (int64_t)tokens[n] * mc.bigram_mul_cur) % mc.bigram_buckets);
+      m->last_tok[sl] = tokens[n];
+    }
     m->length[sl] += counts[e];
   }
   es[E] = N;
   for (int i = 0; i < n_want; i++) wr[i] = want[i];
-  const size_t ints = 4 * (size_t)N + 3 * (size_t)E + 1 + n_want;
+  const size_t ints = 5 * (size_t)N + 3 * (size_t)E + 1 + n_want;
   CK(cudaMemcpyAsync(m->stage_d, h, ints * 4, cudaMemcpyHostToDevice, s));
   CK(cudaEventRecord(m->staged, s));
   int32_t* d = m->stage_d;
   int max_len = 0, row_tiles = 0;
   for (int e = 0; e < E; e++) { max_len = counts[e] > max_len ? counts[e] : max_len; row_tiles += (counts[e] + AT_ROWS - 1) / AT_ROWS; }
-  Batch b{d, d + N, d + 2 * N, d + 3 * N, d + 4 * N, d + 4 * N + E + 1, d + 4 * N + 2 * E + 1, m->bt_d, N, E, m->max_pages, max_len, row_tiles};
-  const int32_t* want_dev = d + 4 * N + 3 * E + 1;
+  Batch b{d, d + N, d + 2 * N, d + 3 * N, d + 5 * N, d + 5 * N + E + 1, d + 5 * N + 2 * E + 1, m->bt_d, N, E, m->max_pages, max_len, row_tiles, d + 4 * N};
+  const int32_t* want_dev = d + 5 * N + 3 * E + 1;
   auto run = [&](float* lg) {
     if (m->cfg.dtype == DN_SEQ_F32) return step_T<float>(m, b, n_want, want_dev, lg, trace, s);
     return step_T<bf16>(m, b, n_want, want_dev, lg, trace, s);

@@ -21,6 +21,11 @@
 //   * (dn_seq_latent.cuh) latent attention: one compressed row per token in the cache, queries absorbed into it
 //   * a sliding-window mask beside the block mask; rotary pairs interleaved or half apart
 //   * RMS norm on a sublayer's output only (the sublayers read the residual itself)
+//   * layer norm with weight and bias; a causal convolution over time on every sublayer's input with carried rows; a
+//     hashed bigram row added to the embedding; RMS norm per head on q and k; rotary frequencies scaled by
+//     interpolation; a query scale that grows with the logarithm of the position; values that are the keys
+//   * a sliding window followed by mean-pooled blocks of the tokens that have left it (one softmax over both)
+//   * (dn_seq_gdelta.cuh) generalized delta rule with a decay and a removal rate per key channel
 // T is the storage type of weights and activations (bf16 or float); sums, norms, scores, positions, gates and
 // states are fp32 in both.
 #pragma once
@@ -114,6 +119,7 @@ struct Batch {
   const int32_t* bt;         // [slots][max_pages] page of each 64-token block
   int N, E, max_pages;
   int max_len, row_tiles;    // longest entry of the step; sum over entries of ceil(tokens / 64)
+  const int32_t* brow;       // [N]   row of the bigram table the token's embedding adds (null: the model has none)
 };
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -122,12 +128,15 @@ struct Batch {
 // hout != null: also in the products' number format (models whose sublayers read the residual without a norm)
 template <class T>
 __global__ void k_embed(const T* __restrict__ embed, Batch b, float scale, int W, int S1, float* __restrict__ xs, const T* __restrict__ nw,
-                        const T* __restrict__ nb, const T* __restrict__ nalpha, float* __restrict__ x0, T* __restrict__ hout) {
+                        const T* __restrict__ nb, const T* __restrict__ nalpha, float* __restrict__ x0, T* __restrict__ hout,
+                        const T* __restrict__ bigram) {
   const int n = blockIdx.x;
   const size_t row = (size_t)b.tok[n] * W;
   const float alpha = nalpha ? ldf(nalpha) : 0.f;
+  const T* brow = bigram ? bigram + (size_t)b.brow[n] * W : nullptr;
   for (int c = threadIdx.x; c < W; c += blockDim.x) {
     float v = ldf(embed + row + c) * scale;
+    if (brow) v += ldf(brow + c);      // the hashed (previous token, token) row, summed in fp32
     if (nalpha) v = dyt_f(v, alpha, nw, nb, c);
     for (int s = 0; s < S1; s++) xs[((size_t)s * b.N + n) * W + c] = v;
     if (x0) x0[(size_t)n * W + c] = v;
@@ -141,7 +150,7 @@ __global__ void k_embed(const T* __restrict__ embed, Batch b, float scale, int W
 template <class T>
 __global__ void k_read_norm(const float* __restrict__ xs, int N, int W, int S, const T* __restrict__ hc_in, const T* __restrict__ nw,
                             int one_plus, int sum_all, float eps, const int32_t* __restrict__ rows, T* __restrict__ h,
-                            const T* __restrict__ nb, const T* __restrict__ nalpha) {
+                            const T* __restrict__ nb, const T* __restrict__ nalpha, int layer_norm) {
   extern __shared__ __align__(16) float sm[];
   float* u = sm;            // [W]
   float* red = sm + W;      // [33]
@@ -172,6 +181,17 @@ __global__ void k_read_norm(const float* __restrict__ xs, int N, int W, int S, c
     __syncthreads();
     const float alpha = ldf(nalpha);
     for (int c = threadIdx.x; c < W; c += blockDim.x) stf(h + (size_t)r * W + c, dyt_f(u[c], alpha, nw, nb, c));
+    return;
+  }
+  if (layer_norm) {    // (u - mean) / sqrt(variance + eps) * w + b: the mean first, then the mean of the squared deviations
+    __syncthreads();
+    float su = 0.f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) su += u[c];
+    const float mean = block_sum(su, red) / (float)W;
+    float sd = 0.f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) { const float d = u[c] - mean; sd += d * d; }
+    const float rinv = 1.f / sqrtf(block_sum(sd, red) / (float)W + eps);
+    for (int c = threadIdx.x; c < W; c += blockDim.x) stf(h + (size_t)r * W + c, (u[c] - mean) * rinv * ldf(nw + c) + ldf(nb + c));
     return;
   }
   ss = block_sum(ss, red);
@@ -271,6 +291,11 @@ __global__ void k_loop_cat(const float* __restrict__ x, const float* __restrict_
   const int c = (int)(i % (2 * W));
   stf(cat + i, c < W ? x[n * W + c] : x0[n * W + c - W]);
 }
+// logits <- s logits
+__global__ void k_scale(float* __restrict__ z, size_t n, float s) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) z[i] *= s;
+}
 // logits <- cap tanh(logits / cap)
 __global__ void k_softcap(float* __restrict__ z, size_t n, float cap) {
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -329,6 +354,27 @@ __global__ void k_rms_join(float* __restrict__ x, int W, const float* __restrict
     x[base + c] = xn;
     if (hout) stf(hout + base + c, xn);
   }
+}
+
+// The two halves of a parallel mixer join the plain residual, each through an RMS norm of its own over the width:
+//   x <- x + a y / rms(y) w1 + b y2 / rms(y2) w2        (plain weights)
+// One block per token, sums in the fixed order of k_rms_join.
+template <class T>
+__global__ void k_rms2_join(float* __restrict__ x, int W, const float* __restrict__ y, float a, const T* __restrict__ w1, const float* __restrict__ y2,
+                            float b, const T* __restrict__ w2, float eps) {
+  __shared__ float red[33];
+  const size_t base = (size_t)blockIdx.x * W;
+  float s1 = 0.f, s2 = 0.f;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    const float u = y[base + c], v = y2[base + c];
+    s1 += u * u;
+    s2 += v * v;
+  }
+  s1 = block_sum(s1, red);
+  s2 = block_sum(s2, red);
+  const float r1 = a / sqrtf(s1 / (float)W + eps), r2 = b / sqrtf(s2 / (float)W + eps);
+  for (int c = threadIdx.x; c < W; c += blockDim.x)
+    x[base + c] += y[base + c] * r1 * ldf(w1 + c) + y2[base + c] * r2 * ldf(w2 + c);
 }
 
 // sum of the streams (inspection hook)
@@ -551,16 +597,41 @@ __global__ void k_conv_carry(CarrySrc<T> src, int taps, Batch b, T* __restrict__
   for (int j = 0; j < m; j++) st[(size_t)j * ldst + c] = keep[j];
 }
 
+// A sublayer's input passes a causal convolution over time: h[n] = hn[n] + sum_j w[:, j] hn[n - taps + 1 + j], rows
+// before the entry's first one from the slot's carried rows (zeros in a fresh slot).  One block per token.
+// carry != 0 (steps in which every entry brings one token): the token's row also becomes the newest carried row;
+// larger steps run k_conv_carry afterwards.  A thread reads and writes its own columns only.
+template <class T>
+__global__ void k_canon(const T* __restrict__ hn, const T* __restrict__ cw, int taps, Batch b, int W, T* __restrict__ state, size_t slot_stride,
+                        T* __restrict__ h, int carry) {
+  const int n = blockIdx.x, local = n - b.first[n];
+  T* st = state + (size_t)b.slot[n] * slot_stride;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    float a = 0.f;
+    for (int j = 0; j < taps; j++) a += ldf(cw + (size_t)c * taps + j) * conv_in(hn, W, c, n, local, taps - 1 - j, (const T*)st, W, taps);
+    stf(h + (size_t)n * W + c, ldf(hn + (size_t)n * W + c) + a);
+    if (carry) {
+      for (int j = 0; j + 2 < taps; j++) st[(size_t)j * W + c] = st[(size_t)(j + 1) * W + c];
+      if (taps > 1) st[(size_t)(taps - 2) * W + c] = hn[(size_t)n * W + c];
+    }
+  }
+}
+
 struct AttnPrep {
   int H, G, dk, dv, taps, rot;       // heads, kv heads, key dim, value dim, conv taps (0: none), rotated dims
   int own_kv;                        // 0: keys / values come from another layer's pages
-  int norm;                          // 0: q and k pass without the RMS norm
+  int norm;                          // 0: q and k pass without the RMS norm; 1: over the whole projection; 2: per head, one weight [dk]
   float eps;
   const float* inv_freq;             // [rot/2]
+  int own_v;                         // 0: the values are the keys (nothing goes to the value pool)
+  int half;                          // 1: rotary pairs (i, i + rot / 2), else (2i, 2i + 1)
+  float mscale;                      // cos and sin are multiplied by this
+  float qt_coef; int qt_every;       // q times 1 + qt_coef ln(floor((p + 1) / qt_every) + 1) (qt_every 0: no)
 };
 
-// attention mixer, between the projections and the scores: conv -> RMS norm over the whole q (k) projection ->
-// rotary -> q to scratch, k / v into the sequence's pages.  One block per token.
+// attention mixer, between the projections and the scores: conv -> RMS norm (over the whole q / k projection or per
+// head) -> rotary (angles, cos and sin fp32, one table a token) -> query scale -> q to scratch, k / v into the
+// sequence's pages.  One block per token.  Shared memory: Cq + Ck + 34 + H + G + rot floats.
 template <class T>
 __global__ void k_attn_prep(AttnPrep a, Batch b, const T* __restrict__ Uq, const T* __restrict__ Uk, const T* __restrict__ Uv,
                             const T* __restrict__ cwq, const T* __restrict__ cwk, const T* __restrict__ cwv, const T* __restrict__ nq,
@@ -568,10 +639,14 @@ __global__ void k_attn_prep(AttnPrep a, Batch b, const T* __restrict__ Uq, const
                             T* __restrict__ kpool, T* __restrict__ vpool) {
   extern __shared__ float sm[];
   // a layer that borrows its keys and values projects and carries q only
-  const int Cq = a.H * a.dk, Ck = a.own_kv ? a.G * a.dk : 0, Cv = a.own_kv ? a.G * a.dv : 0, ldst = Cq + Ck + Cv;
+  const int Cq = a.H * a.dk, Ck = a.own_kv ? a.G * a.dk : 0, Cv = (a.own_kv && a.own_v) ? a.G * a.dv : 0, ldst = Cq + Ck + Cv;
+  const int HG = a.H + (a.own_kv ? a.G : 0);
   float* qs = sm;
   float* ks = sm + Cq;
-  float* red = ks + Ck;
+  float* red = ks + Ck;           // [34]
+  float* hinv = red + 34;         // [H + G] inverse RMS of each head (norm 2)
+  float* cst = hinv + a.H + a.G;  // [rot / 2] cos, then [rot / 2] sin
+  float* snt = cst + a.rot / 2;
   const int n = blockIdx.x, slot = b.slot[n], p = b.pos[n];
   const int local = n - b.first[n];   // rows of this step that precede the token in its sequence
   const T* st = cstate + (size_t)slot * slot_stride;
@@ -590,44 +665,99 @@ __global__ void k_attn_prep(AttnPrep a, Batch b, const T* __restrict__ Uq, const
     }
     sk = block_sum(sk, red);
   }
-  const float rq = a.norm ? 1.f / sqrtf(sq / (float)Cq + a.eps) : 1.f, rk = a.norm ? 1.f / sqrtf(sk / (float)Ck + a.eps) : 1.f;
+  for (int i = threadIdx.x; i < a.rot / 2; i += blockDim.x) {
+    float sn, cs;
+    sincosf((float)p * a.inv_freq[i], &sn, &cs);
+    cst[i] = cs * a.mscale;
+    snt[i] = sn * a.mscale;
+  }
+  if (a.norm == 2) {      // one warp a head: lanes over the head's dims in ascending order, then the lanes pairwise
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    for (int hh = w; hh < HG; hh += nw) {
+      const float* src = hh < a.H ? qs + hh * a.dk : ks + (hh - a.H) * a.dk;
+      float ss = 0.f;
+      for (int d = lane; d < a.dk; d += 32) ss += src[d] * src[d];
+      ss = warp_sum(ss);
+      if (lane == 0) hinv[hh] = 1.f / sqrtf(ss / (float)a.dk + a.eps);
+    }
+  }
+  __syncthreads();
+  const float rq = a.norm == 1 ? 1.f / sqrtf(sq / (float)Cq + a.eps) : 1.f, rk = (a.norm == 1 && a.own_kv) ? 1.f / sqrtf(sk / (float)Ck + a.eps) : 1.f;
+  const float qt = a.qt_every > 0 ? 1.f + a.qt_coef * logf((float)((p + 1) / a.qt_every + 1)) : 1.f;
   const int page = b.bt[(size_t)slot * b.max_pages + p / PAGE], prow = p % PAGE;
-  const int halfk = a.dk / 2;
-  // pairs (2i, 2i+1) of every head; odd dk leaves its last dim to the tail loop below
-  for (int e = threadIdx.x; e < (a.H + (a.own_kv ? a.G : 0)) * halfk; e += blockDim.x) {
-    const int hh = e / halfk, i = e % halfk;
+  T* krow = kpool + ((size_t)page * PAGE + prow) * Ck;
+  // element d of head hh (q heads first, then k heads) after the norm
+  auto val = [&](int hh, int d) -> float {
     const bool isq = hh < a.H;
-    const int head = isq ? hh : hh - a.H;
-    const int c0 = head * a.dk + 2 * i;
-    float x0, x1;
-    if (!a.norm) { x0 = isq ? qs[c0] : ks[c0]; x1 = isq ? qs[c0 + 1] : ks[c0 + 1]; }
-    else if (isq) { x0 = qs[c0] * rq * ldf(nq + c0); x1 = qs[c0 + 1] * rq * ldf(nq + c0 + 1); }
-    else { x0 = ks[c0] * rk * ldf(nk + c0); x1 = ks[c0 + 1] * rk * ldf(nk + c0 + 1); }
-    if (2 * i + 1 < a.rot) {
-      const float ang = (float)p * a.inv_freq[i];
-      float sn, cs;
-      sincosf(ang, &sn, &cs);
-      const float y0 = x0 * cs - x1 * sn, y1 = x1 * cs + x0 * sn;
-      x0 = y0; x1 = y1;
+    const int c = (isq ? hh : hh - a.H) * a.dk + d;
+    const float x = isq ? qs[c] : ks[c];
+    if (a.norm == 0) return x;
+    if (a.norm == 1) return isq ? x * rq * ldf(nq + c) : x * rk * ldf(nk + c);
+    return x * hinv[hh] * ldf((isq ? nq : nk) + d);
+  };
+  auto put = [&](int hh, int d, float y) {
+    if (hh < a.H) stf(qout + (size_t)n * Cq + hh * a.dk + d, a.qt_every > 0 ? y * qt : y);
+    else stf(krow + (hh - a.H) * a.dk + d, y);
+  };
+  if (a.half) {       // pairs (i, i + rot / 2); dims from rot up pass
+    const int hr = a.rot / 2;
+    for (int e = threadIdx.x; e < HG * a.dk; e += blockDim.x) {
+      const int hh = e / a.dk, d = e % a.dk;
+      float y = val(hh, d);
+      if (d < hr) y = y * cst[d] - val(hh, d + hr) * snt[d];
+      else if (d < a.rot) y = y * cst[d - hr] + val(hh, d - hr) * snt[d - hr];
+      put(hh, d, y);
     }
-    if (isq) { stf(qout + (size_t)n * Cq + c0, x0); stf(qout + (size_t)n * Cq + c0 + 1, x1); }
-    else {
-      T* kr = kpool + ((size_t)page * PAGE + prow) * Ck;
-      stf(kr + c0, x0); stf(kr + c0 + 1, x1);
+  } else {
+    const int halfk = a.dk / 2;
+    // pairs (2i, 2i+1) of every head; odd dk leaves its last dim to the tail loop below
+    for (int e = threadIdx.x; e < HG * halfk; e += blockDim.x) {
+      const int hh = e / halfk, i = e % halfk;
+      float x0 = val(hh, 2 * i), x1 = val(hh, 2 * i + 1);
+      if (2 * i + 1 < a.rot) {
+        const float y0 = x0 * cst[i] - x1 * snt[i], y1 = x1 * cst[i] + x0 * snt[i];
+        x0 = y0; x1 = y1;
+      }
+      put(hh, 2 * i, x0);
+      put(hh, 2 * i + 1, x1);
     }
+    if (a.dk & 1)
+      for (int hh = threadIdx.x; hh < HG; hh += blockDim.x) put(hh, a.dk - 1, val(hh, a.dk - 1));
   }
-  if (a.dk & 1) {
-    for (int hh = threadIdx.x; hh < a.H + (a.own_kv ? a.G : 0); hh += blockDim.x) {
-      const bool isq = hh < a.H;
-      const int c = (isq ? hh : hh - a.H) * a.dk + a.dk - 1;
-      if (isq) stf(qout + (size_t)n * Cq + c, a.norm ? qs[c] * rq * ldf(nq + c) : qs[c]);
-      else stf(kpool + ((size_t)page * PAGE + prow) * Ck + c, a.norm ? ks[c] * rk * ldf(nk + c) : ks[c]);
-    }
-  }
-  if (a.own_kv) {
+  if (Cv > 0) {
     T* vr = vpool + ((size_t)page * PAGE + prow) * Cv;
     for (int c = threadIdx.x; c < Cv; c += blockDim.x)
       stf(vr + c, conv_at(Uv, Cv, cwv, c, n, local, st + Cq + Ck, ldst, a.taps));
+  }
+}
+
+// Mean-pooled blocks behind a sliding window.  Block j of a sequence holds the positions j P .. j P + P - 1; its pooled
+// key (value) is the mean of the P keys (values) as the pages hold them.  A pooled row lives with the page of the
+// block's last position e = j P + P - 1: row j - floor(64 (e / 64) / P) of that page's POOL_ROWS(P) = ceil(64 / P) rows
+// in a pool of its own, so the sequence's block table finds it and a freed page frees its pooled rows.  A query at p
+// with a window of `size` positions sees the blocks j < pooled_seen(p, size, P): those with j P + P - 1 <= p - size.
+__host__ __device__ __forceinline__ int pool_rows(int P) { return (PAGE + P - 1) / P; }
+__device__ __forceinline__ int pooled_seen(int p, int size, int P) { return (P > 0 && p - size + 1 > 0) ? (p - size + 1) / P : 0; }
+__device__ __forceinline__ size_t pooled_row(const int32_t* __restrict__ bt, int j, int P) {
+  const int pg = (j * P + P - 1) / PAGE;
+  return (size_t)bt[pg] * pool_rows(P) + (j - (pg * PAGE) / P);
+}
+// after the step's keys and values are in their pages: the block of every token that ends one ((p + 1) % P == 0) pools
+// it, positions in ascending order.  One block per token.
+template <class T>
+__global__ void k_pool_rows(Batch b, int P, int Ck, int Cv, const T* __restrict__ kpool, const T* __restrict__ vpool, T* __restrict__ pk,
+                            T* __restrict__ pv) {
+  const int n = blockIdx.x, p = b.pos[n];
+  if ((p + 1) % P) return;
+  const int32_t* bt = b.bt + (size_t)b.slot[n] * b.max_pages;
+  const size_t row = pooled_row(bt, (p + 1) / P - 1, P);
+  for (int c = threadIdx.x; c < Ck + Cv; c += blockDim.x) {
+    const bool isk = c < Ck;
+    const int cc = isk ? c : c - Ck, ld = isk ? Ck : Cv;
+    const T* src = isk ? kpool : vpool;
+    float a = 0.f;
+    for (int j = p - P + 1; j <= p; j++) a += ldf(src + ((size_t)bt[j / PAGE] * PAGE + (j % PAGE)) * ld + cc);
+    stf((isk ? pk : pv) + row * ld + cc, a / (float)P);
   }
 }
 
@@ -646,7 +776,12 @@ struct AttnExtra {
   const float* gate;
   int window;      // 1: `chunk` is a sliding window -- a query at p sees the keys p - chunk + 1 .. p
   int v_ld;        // row stride of the value pool in elements (0: G dv); latent attention reads its values out of the key rows
+  int pool;        // > 0 (with window): blocks of this many tokens wholly before the window are seen as one mean key / value each
+  const void* pk;  // their pools [pages][pool_rows(pool)][row], strides as the token pools'
+  const void* pv;
 };
+// keys a query at p sees: the pooled blocks first (virtual indices 0 .. nb - 1), then the tokens lo .. p
+__device__ __forceinline__ int attn_pooled(int p, int chunk, const AttnExtra& ex) { return ex.pool > 0 ? pooled_seen(p, chunk, ex.pool) : 0; }
 // first key a query at position p sees
 __device__ __forceinline__ int attn_lo(int p, int chunk, int window) {
   if (chunk <= 0) return 0;
@@ -694,7 +829,8 @@ __global__ void __launch_bounds__(AT_WARPS * 32) k_attn(Batch b, const T* __rest
   const int n = blockIdx.x, h = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = h / (H / G), slot = b.slot[n], p = b.pos[n];
   const int lo = attn_lo(p, chunk, ex.window);
-  const int nz = attn_splits(p - lo + 1, (int)gridDim.z), z = blockIdx.z;
+  const int nb = attn_pooled(p, chunk, ex), nkeys = nb + p - lo + 1;
+  const int nz = attn_splits(nkeys, (int)gridDim.z), z = blockIdx.z;
   if (z >= nz) return;
   const int Ck = G * dk, Cv = ex.v_ld > 0 ? ex.v_ld : G * dv;
   for (int d = threadIdx.x; d < dk; d += blockDim.x) qs[d] = ldf(q + ((size_t)n * H + h) * dk + d);
@@ -707,11 +843,22 @@ __global__ void __launch_bounds__(AT_WARPS * 32) k_attn(Batch b, const T* __rest
   float m = -INFINITY, l = 0.f, acc[MAXV];
 #pragma unroll
   for (int i = 0; i < MAXV; i++) acc[i] = 0.f;
-  for (int j0 = lo + (z * AT_WARPS + warp) * 32; j0 <= p; j0 += nz * AT_WARPS * 32) {
+  // the row of virtual key v in the key (value) pools
+  auto key_row = [&](int v) -> const T* {
+    if (v < nb) return (const T*)ex.pk + pooled_row(bt, v, ex.pool) * Ck;
+    const int j = lo + v - nb;
+    return kpool + ((size_t)bt[j / PAGE] * PAGE + (j % PAGE)) * Ck;
+  };
+  auto val_row = [&](int v) -> const T* {
+    if (v < nb) return (const T*)ex.pv + pooled_row(bt, v, ex.pool) * Cv;
+    const int j = lo + v - nb;
+    return vpool + ((size_t)bt[j / PAGE] * PAGE + (j % PAGE)) * Cv;
+  };
+  for (int j0 = (z * AT_WARPS + warp) * 32; j0 < nkeys; j0 += nz * AT_WARPS * 32) {
     const int j = j0 + lane;
     float s = -INFINITY;
-    if (j <= p) {
-      const T* kr = kpool + ((size_t)bt[j / PAGE] * PAGE + (j % PAGE)) * Ck + g * dk;
+    if (j < nkeys) {
+      const T* kr = key_row(j) + g * dk;
       float d0 = 0.f;
       if (kvec) {
 #pragma unroll 8
@@ -729,16 +876,15 @@ __global__ void __launch_bounds__(AT_WARPS * 32) k_attn(Batch b, const T* __rest
     }
     const float mn = fmaxf(m, warp_max(s));
     const float corr = expf(m - mn);      // exp(-inf) = 0 on the warp's first tile
-    const float pj = j <= p ? expf(s - mn) : 0.f;
+    const float pj = j < nkeys ? expf(s - mn) : 0.f;
     l = l * corr + warp_sum(pj);
 #pragma unroll
     for (int i = 0; i < MAXV; i++) acc[i] *= corr;
-    const int cnt = min(32, p - j0 + 1);
+    const int cnt = min(32, nkeys - j0);
 #pragma unroll 4
     for (int t = 0; t < cnt; t++) {
       const float pt = __shfl_sync(0xffffffffu, pj, t);
-      const int jj = j0 + t;
-      const T* vr = vpool + ((size_t)bt[jj / PAGE] * PAGE + (jj % PAGE)) * Cv + g * dv + lane * VPL;
+      const T* vr = val_row(j0 + t) + g * dv + lane * VPL;
 #pragma unroll
       for (int i0 = 0; i0 < MAXV; i0 += 8) {
         if (i0 < vcnt) {
@@ -783,7 +929,7 @@ template <class T>
 __global__ void k_attn_merge(Batch b, int H, int dv, int chunk, int zmax, AttnExtra ex, const float* __restrict__ part_g, T* __restrict__ out) {
   const int n = blockIdx.x, h = blockIdx.y, p = b.pos[n];
   const int lo = attn_lo(p, chunk, ex.window);
-  const int nz = attn_splits(p - lo + 1, zmax);
+  const int nz = attn_splits(attn_pooled(p, chunk, ex) + p - lo + 1, zmax);
   if (nz <= 1) return;
   const int dvp = (dv + 31) / 32 * 32;
   const float* pg = part_g + ((size_t)n * H + h) * zmax * (2 + dvp);
@@ -840,6 +986,20 @@ __device__ __forceinline__ void load_tile64(bf16* __restrict__ dst, const bf16* 
   }
 }
 
+// the same for pooled rows j0 .. j0 + valid - 1 of a sequence, each found through the block table (src: the pool's base plus
+// the head group's offset)
+template <int LDS>
+__device__ __forceinline__ void load_tile64_rows(bf16* __restrict__ dst, const bf16* __restrict__ src, size_t ld, int cols, int valid,
+                                                 const int32_t* __restrict__ bt, int j0, int P) {
+  const int vec = LDS / 8 - 1;
+  for (int e = threadIdx.x; e < 64 * vec; e += blockDim.x) {
+    const int r = e / vec, c = (e % vec) * 8;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < valid && c < cols) v = *reinterpret_cast<const uint4*>(src + pooled_row(bt, j0 + r, P) * ld + c);
+    *reinterpret_cast<uint4*>(dst + r * LDS + c) = v;
+  }
+}
+
 constexpr int AT_ROWS = 64;      // query rows of a block, and keys of a tile (= PAGE)
 template <int DKP, int DVP>
 __global__ void __launch_bounds__(128) k_attn_tiles(Batch b, const bf16* __restrict__ q, const bf16* __restrict__ kpool,
@@ -881,12 +1041,23 @@ __global__ void __launch_bounds__(128) k_attn_tiles(Batch b, const bf16* __restr
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
   const int32_t* bt = b.bt + (size_t)b.ent_slot[e] * b.max_pages;
   const int lo_tile = attn_lo(p_first, chunk, ex.window);
-  for (int j0 = (lo_tile / PAGE) * PAGE; j0 <= p_last; j0 += PAGE) {
-    const size_t prow = (size_t)bt[j0 / PAGE] * PAGE;
-    const int kvalid = min(PAGE, p_last - j0 + 1);      // rows of the page beyond the last query's position are not read
+  // pooled blocks behind the window come first, 64 to a tile, in ascending block order; then the pages of the tokens
+  const int nb0 = p0 >= 0 ? attn_pooled(p0, chunk, ex) : 0, nb1 = p1 >= 0 ? attn_pooled(p1, chunk, ex) : 0;
+  const int nb_last = attn_pooled(p_last, chunk, ex), pool_tiles = (nb_last + AT_ROWS - 1) / AT_ROWS;
+  const int tok0 = (lo_tile / PAGE) * PAGE, tok_tiles = p_last >= tok0 ? (p_last - tok0) / PAGE + 1 : 0;
+  for (int it = 0; it < pool_tiles + tok_tiles; it++) {
+    const bool pooled = it < pool_tiles;
+    const int j0 = pooled ? it * AT_ROWS : tok0 + (it - pool_tiles) * PAGE;
     __syncthreads();
-    load_tile64<LQ>(Ks, kpool + prow * Ck + (size_t)g * dk, (size_t)Ck, dk, kvalid);
-    load_tile64<LV>(Vs, vpool + prow * Cv + (size_t)g * dv, (size_t)Cv, dv, kvalid);
+    if (pooled) {
+      load_tile64_rows<LQ>(Ks, (const bf16*)ex.pk + (size_t)g * dk, (size_t)Ck, dk, min(AT_ROWS, nb_last - j0), bt, j0, ex.pool);
+      load_tile64_rows<LV>(Vs, (const bf16*)ex.pv + (size_t)g * dv, (size_t)Cv, dv, min(AT_ROWS, nb_last - j0), bt, j0, ex.pool);
+    } else {
+      const size_t prow = (size_t)bt[j0 / PAGE] * PAGE;
+      const int kvalid = min(PAGE, p_last - j0 + 1);      // rows of the page beyond the last query's position are not read
+      load_tile64<LQ>(Ks, kpool + prow * Ck + (size_t)g * dk, (size_t)Ck, dk, kvalid);
+      load_tile64<LV>(Vs, vpool + prow * Cv + (size_t)g * dv, (size_t)Cv, dv, kvalid);
+    }
     __syncthreads();
     if (!warp_live) continue;
     float sc[8][4];
@@ -911,8 +1082,8 @@ __global__ void __launch_bounds__(128) k_attn_tiles(Batch b, const bf16* __restr
         const int key = j0 + j * 8 + (lane & 3) * 2 + i;
         float a0 = sc[j][i] * scale, a1 = sc[j][2 + i] * scale;
         if (ex.softcap > 0.f) { a0 = ex.softcap * tanhf(a0 / ex.softcap); a1 = ex.softcap * tanhf(a1 / ex.softcap); }
-        sc[j][i] = (key <= p0 && key >= lo0) ? a0 : -INFINITY;
-        sc[j][2 + i] = (key <= p1 && key >= lo1) ? a1 : -INFINITY;
+        sc[j][i] = (pooled ? key < nb0 : (key <= p0 && key >= lo0)) ? a0 : -INFINITY;
+        sc[j][2 + i] = (pooled ? key < nb1 : (key <= p1 && key >= lo1)) ? a1 : -INFINITY;
         mx0 = fmaxf(mx0, sc[j][i]);
         mx1 = fmaxf(mx1, sc[j][2 + i]);
       }
@@ -1140,17 +1311,21 @@ __global__ void __launch_bounds__(32 * P) k_delta_rule(Batch b, int H, int G, in
 }
 
 // read-out of the recurrence: per head o / rms(o) * w * silu(gate) -> T.  One warp per (token, head).
-// wstride: 0 when the heads share one weight [dv], dv when every head has its own ([H, dv])
+// wstride: 0 when the heads share one weight [dv], dv when every head has its own ([H, dv]); gate_sigmoid: the gate
+// goes through a sigmoid instead of silu
 template <class T>
 __global__ void __launch_bounds__(32) k_delta_out(const float* __restrict__ o, const T* __restrict__ gate, const T* __restrict__ nw, int H,
-                                                  int dv, float eps, T* __restrict__ out, int wstride) {
+                                                  int dv, float eps, T* __restrict__ out, int wstride, int gate_sigmoid = 0) {
   const int n = blockIdx.x, h = blockIdx.y, lane = threadIdx.x;
   const size_t base = ((size_t)n * H + h) * dv;
   float ss = 0.f;
   for (int d = lane; d < dv; d += 32) ss += o[base + d] * o[base + d];
   ss = warp_sum(ss);
   const float r = 1.f / sqrtf(ss / (float)dv + eps);
-  for (int d = lane; d < dv; d += 32) stf(out + base + d, o[base + d] * r * ldf(nw + (size_t)h * wstride + d) * silu_f(ldf(gate + base + d)));
+  for (int d = lane; d < dv; d += 32) {
+    const float gz = ldf(gate + base + d);
+    stf(out + base + d, o[base + d] * r * ldf(nw + (size_t)h * wstride + d) * (gate_sigmoid ? sigmoid_f(gz) : silu_f(gz)));
+  }
 }
 
 }  // namespace dnseq

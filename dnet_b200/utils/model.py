@@ -29,6 +29,7 @@ NORM_RE = re.compile(r"^model\.norm\.(.+)$")
 # checkpoints of the layer-list families (core/models/seqmix.py): l<i>.<tensor>, embed, final.norm, head
 SEQ_LAYER_RE = re.compile(r"^l(\d+)\.(.+)$")
 SEQ_API = {"embed": "embed_tokens", "final.norm": "norm", "head": "lm_head"}
+SEQ_EMBED_EXTRA = ("bigram",)      # further tables the embedding reads
 SEQ_MODEL_RE = re.compile(r"^(embed|final|head|loop)\.(.+)$")
 
 
@@ -141,6 +142,8 @@ def _classify(details: Dict[str, TensorInfo], weight_info, embed_tokens, lm_head
             weight_info[int(layer_idx)][suffix] = val
         elif key in SEQ_API:
             {"embed_tokens": embed_tokens, "norm": norm, "lm_head": lm_head}[SEQ_API[key]]["weight"] = val
+        elif key in SEQ_EMBED_EXTRA:
+            embed_tokens["seq:" + key] = val
         elif m := SEQ_MODEL_RE.match(key):      # other model tensors of a layer-list family, under their checkpoint names
             {"embed": embed_tokens, "final": norm, "head": lm_head, "loop": norm}[m.group(1)]["seq:" + key] = val
         else:

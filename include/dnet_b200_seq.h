@@ -1,9 +1,11 @@
 /*
  * dnet_b200_seq.h -- C ABI of libdnet_b200_seq.so: the batched step of decoder models whose layers are a
- * sequence mixer (softmax attention over a paged cache -- block-masked or sliding-window, capped, with a sink and head
- * gates --, latent attention that caches one compressed row per token, a gated delta-rule recurrence, decayed
- * outer-product recurrences, or attention beside one of those) plus an optional dense, gated or routed feed-forward,
- * tied together by S residual streams; a span of layers may run several times on the same weights.
+ * sequence mixer (softmax attention over a paged cache -- block-masked or sliding-window, the window optionally followed
+ * by mean-pooled blocks of older tokens, capped, with a sink and head gates --, latent attention that caches one
+ * compressed row per token, a gated delta-rule recurrence, a generalized delta rule with a decay and a removal rate per
+ * key channel, decayed outer-product recurrences, or attention beside one of those) plus an optional dense, gated or
+ * routed feed-forward, tied together by S residual streams; a span of layers may run several times on the same weights;
+ * every sublayer's input may pass a short causal convolution first, and the embedding may add a hashed bigram row.
  *
  * Same conventions as dnet_b200.h: plain C, opaque handles, 0 or a negative DN_E* code, dn_seq_last_error() for
  * the text, caller-owned streams and buffers, weights BORROWED by pointer.  One handle serves one compute thread.
@@ -38,6 +40,14 @@ extern "C" {
 
 #define DN_NORM_RMS 0       /* x / sqrt(mean(x^2) + eps) * w  (or 1 + w) */
 #define DN_NORM_DYT 1       /* tanh(alpha x) * w + b, elementwise */
+#define DN_NORM_LAYER 2     /* (x - mean) / sqrt(variance + eps) * w + b */
+
+#define DN_QKNORM_NONE 0
+#define DN_QKNORM_WHOLE 1   /* RMS norm over the whole q (k) projection, weight [heads dim] */
+#define DN_QKNORM_HEAD 2    /* RMS norm over each head's dim, one weight [dim] for all heads */
+
+#define DN_RIGHT_GLA 0      /* right half of DN_MIX_PARALLEL: gated linear attention, M <- diag(d) M + k v^T */
+#define DN_RIGHT_GDELTA 1   /* generalized delta rule: S <- diag(w) S - (a u)(u^T S) + k v^T with u = k / |k|, read after the update */
 
 #define DN_MLP_DENSE 0      /* gelu_tanh(gate) * up -> down, or (ff_act) an ungated activation between up and down */
 #define DN_MLP_MOE 1        /* routed GLU experts (+ an optional shared one) */
@@ -69,7 +79,7 @@ typedef struct dn_seq_layer_cfg {
   int32_t kv_from;     /* attention: layer whose pages hold this layer's keys and values (-1: its own) */
   int32_t ff;          /* feed-forward width, of one expert for DN_MLP_MOE (0: the layer has no feed-forward) */
   /* attention (also the attention half of DN_MIX_PARALLEL) */
-  int32_t qk_norm;     /* 1: RMS norm over the whole q and k projections with learned weights */
+  int32_t qk_norm;     /* DN_QKNORM_*: RMS norm of q and k with learned weights, before rotation */
   float softcap;       /* scores: cap * tanh(score / cap) after the scale (0: none) */
   int32_t sink;        /* 1: the softmax denominator holds one more term exp(sink_h), a learned number per head */
   int32_t out_gate;    /* 1: head h's output is multiplied by sigmoid(w_h . x), one gate per head */
@@ -98,6 +108,18 @@ typedef struct dn_seq_layer_cfg {
   int32_t groups, groups_keep;   /* DN_ROUTER_SCORED: experts (identity ones included) in `groups` equal runs, the best kept (0: no groups) */
   float router_scale;
   int32_t shared_gate; /* 1: the shared expert's output is multiplied by sigmoid(w . h), one number a token */
+  /* attention */
+  int32_t v_is_k;      /* 1: the values are the keys as projected (vdim = dim, no value projection, one pool) */
+  float qtemp_coef;    /* queries at position p are multiplied by 1 + qtemp_coef ln(floor((p + 1) / qtemp_every) + 1) (qtemp_every 0: no) */
+  int32_t qtemp_every;
+  int32_t pool;        /* DN_MASK_WINDOW: beside the window's tokens a query sees one mean key / value for each block of `pool` tokens
+                          that lies wholly before the window (0: none) */
+  /* rotary frequencies scaled by interpolation between f / factor (slow dims) and f (fast dims); cos and sin times
+   * 0.1 ln(factor) + 1.  yarn_factor 0: plain frequencies */
+  float yarn_factor, yarn_original, yarn_fast, yarn_slow;
+  /* DN_MIX_PARALLEL */
+  int32_t r_kind;      /* DN_RIGHT_* */
+  int32_t branch_norm; /* 1: each half's output is RMS-normed over the width (weights DN_SQ_L_OUT / DN_SQ_R_OUT) before the scaled sum */
 } dn_seq_layer_cfg;
 
 typedef struct dn_seq_cfg {
@@ -117,6 +139,13 @@ typedef struct dn_seq_cfg {
    * state; before the first layer of each pass x <- W_in [x; x0] with x0 the embedding's output.  loop_times = 0: no loop */
   int32_t loop_start, loop_stop, loop_times;
   int32_t no_pre_norm;       /* 1: sublayers read the residual itself; only their outputs are normed (post_norm) */
+  /* every sublayer's input h becomes h + conv(h), a causal depthwise convolution over time of canon_taps taps whose last
+   * canon_taps - 1 inputs are carried per sequence, layer run and sublayer (0: none) */
+  int32_t canon_taps;
+  /* the embedding adds row (previous token * mul_prev + token * mul_cur) mod buckets of DN_SQ_BIGRAM, row `buckets` for a
+   * sequence's first token; the previous token is carried per sequence (buckets 0: none) */
+  int32_t bigram_buckets, bigram_mul_prev, bigram_mul_cur;
+  float logit_scale;         /* logits are multiplied by this (0: by 1) */
 } dn_seq_cfg;
 
 /* tensors of a layer (dn_seq_bind: layer >= 0) and of the model (layer = -1) */
@@ -144,9 +173,13 @@ enum {
   DN_SQ_DQ, DN_SQ_DQ_NORM, DN_SQ_DKV, DN_SQ_DKV_NORM, DN_SQ_UK, DN_SQ_UV,
   /* biases of a dense feed-forward [ff], [W]; DN_ROUTER_SCORED: correction [experts + identity]; the shared expert's gate [W] */
   DN_SQ_UP_B, DN_SQ_DOWN_B, DN_SQ_ROUTER_CORR, DN_SQ_SH_SG,
+  /* the sublayers' input convolutions [W, canon_taps]; the norms of a parallel mixer's two outputs [W] (branch_norm);
+   * DN_RIGHT_GDELTA: the removal rate's projection [C, W] and bias [C] (DN_SQ_R_Q is the read vector's projection,
+   * DN_SQ_DECAY1 / 2 / _B the decay's, DN_SQ_R_NORM [C] one weight per channel) */
+  DN_SQ_CANON1, DN_SQ_CANON2, DN_SQ_L_OUT, DN_SQ_R_OUT, DN_SQ_R_A, DN_SQ_R_AB,
   DN_SQ_COUNT,
   DN_SQ_EMBED = 100, DN_SQ_FINAL_NORM, DN_SQ_HEAD, DN_SQ_FINAL_NORM_B, DN_SQ_FINAL_NORM_ALPHA,
-  DN_SQ_EMBED_NORM, DN_SQ_EMBED_NORM_B, DN_SQ_EMBED_NORM_ALPHA, DN_SQ_LOOP_IN
+  DN_SQ_EMBED_NORM, DN_SQ_EMBED_NORM_B, DN_SQ_EMBED_NORM_ALPHA, DN_SQ_LOOP_IN, DN_SQ_BIGRAM
 };
 /* matrices of a routed expert (dn_seq_bind_expert) */
 enum { DN_SQ_E_GATE = 0, DN_SQ_E_UP, DN_SQ_E_DOWN };
@@ -190,6 +223,7 @@ enum {
   DN_SEQ_PH_MOE_UP, DN_SEQ_PH_MOE_DOWN,
   DN_SEQ_PH_LATENT_IN,    /* latent attention: the cached row, rotary, queries absorbed into the latent space */
   DN_SEQ_PH_LATENT_OUT,   /* latent attention: the heads' outputs taken out of the latent space */
+  DN_SEQ_PH_CANON,        /* the sublayers' input convolutions and their carried rows */
   DN_SEQ_PH_COUNT
 };
 int dn_seq_profile(dn_seq_model* m, int on);

@@ -64,7 +64,8 @@ def test_header_and_binding_agree():
     spell = {"OUT_NORM": "mix.norm", "NORM1": "norm1", "NORM2": "norm2", "GATE": "mlp.gate", "UP": "mlp.up", "DOWN": "mlp.down",
              "HEAD_GATE": "head_gate", "SINK": "sink", "BONUS": "bonus", "DECAY1": "decay1", "DECAY2": "decay2", "DECAY_B": "decay.b",
              "ROUTER": "router", "ROUTER_B": "router.b", "SH_GATE": "shared.gate", "SH_UP": "shared.up", "SH_DOWN": "shared.down",
-             "UP_B": "mlp.up.b", "DOWN_B": "mlp.down.b", "ROUTER_CORR": "router.corr", "SH_SG": "shared.sg"}
+             "UP_B": "mlp.up.b", "DOWN_B": "mlp.down.b", "ROUTER_CORR": "router.corr", "SH_SG": "shared.sg",
+             "CANON1": "canon1", "CANON2": "canon2", "L_OUT": "l.out"}
     for i, name in enumerate(order):
         n = name[len("DN_SQ_"):]
         if n in spell:
@@ -76,7 +77,7 @@ def test_header_and_binding_agree():
         assert _seqabi.LAYER_SLOT[want] == i, (name, want)
     model = [n.strip().split("=")[0].strip() for n in txt.split("DN_SQ_COUNT,", 1)[1].split("}", 1)[0].replace("\n", " ").split(",") if n.strip()]
     assert [_seqabi.MODEL_SLOT[k] for k in ("embed", "final.norm", "head", "final.norm.b", "final.norm.alpha", "embed.norm", "embed.norm.b",
-                                           "embed.norm.alpha", "loop.in")] == list(range(100, 100 + len(model)))
+                                           "embed.norm.alpha", "loop.in", "bigram")] == list(range(100, 100 + len(model)))
 
 
 def _filinex_cfg():
