@@ -428,6 +428,9 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     if args.config == "lutesun":
         from bench_lutesun import run_lutesun
         return run_lutesun(args, rank, local_rank, world)
+    if args.config == "vulanex":
+        from bench_vulanex import run_vulanex
+        return run_vulanex(args, rank, local_rank, world)
     if args.config == "prefill":
         from bench_prefill import run_prefill
         return run_prefill(args, rank, local_rank, world)
@@ -479,9 +482,9 @@ def main():
                     help="N>1: lm_head tensor-parallel over the ring's shards (auto: rings of >= 4 shards)")
     ap.add_argument("--sched-rounds", type=int, default=8, help="decode rounds per schedule frame (head shard's RingAdapter)")
     ap.add_argument("--sched-depth", type=int, default=4, help="schedule frames in flight")
-    ap.add_argument("--config", default="decode", choices=["decode", "swap", "prefill", "moe", "seqmix", "filinex", "lutesun"],
+    ap.add_argument("--config", default="decode", choices=["decode", "swap", "prefill", "moe", "seqmix", "filinex", "lutesun", "vulanex"],
                     help="decode: BASELINE configs[1] (the bench contract); swap: configs[3], Llama-3-70B layer swap (bench_swap.py); "
-                         "lutesun: the Lutesun family beside Filinex (bench_lutesun.py; uses --seqmix-sizes / --seqmix-prompt); filinex: the Filinex family beside Moputar (bench_filinex.py; uses --seqmix-sizes / --seqmix-prompt); seqmix: a layer-list model (Moputar) beside the llama family at equal size (bench_seqmix.py)")
+                         "vulanex: the Vulanex family beside Moputar (bench_vulanex.py; uses --seqmix-sizes / --seqmix-prompt); lutesun: the Lutesun family beside Filinex (bench_lutesun.py; uses --seqmix-sizes / --seqmix-prompt); filinex: the Filinex family beside Moputar (bench_filinex.py; uses --seqmix-sizes / --seqmix-prompt); seqmix: a layer-list model (Moputar) beside the llama family at equal size (bench_seqmix.py)")
     ap.add_argument("--seqmix-sizes", default="1k,2k,4k", help="--config seqmix: comma list of 1k, 2k, 4k (model width)")
     ap.add_argument("--seqmix-prompt", type=int, default=2048, help="--config seqmix: prompt tokens (one step)")
     ap.add_argument("--seqmix-repeats", type=int, default=2, help="--config seqmix: repeats of (attention, attention on shared pages, delta)")

@@ -962,15 +962,17 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
   auto norm_in = [&](SeqLayer& l, const Run& run, int q) -> int {
     auto w = [&](int i) { return (const T*)l.w[i]; };
     const int nrm = q == 0 ? DN_SQ_NORM1 : DN_SQ_NORM2, nb = q == 0 ? DN_SQ_NORM1_B : DN_SQ_NORM2_B, na = q == 0 ? DN_SQ_NORM1_ALPHA : DN_SQ_NORM2_ALPHA;
-    T* dst = taps > 0 ? (T*)m->hn : (T*)m->h;
+    const bool fused = taps > 0 && b.max_len == 1;      // every entry one token: the norm kernel convolves and carries the row itself
+    T* dst = taps > 0 && !fused ? (T*)m->hn : (T*)m->h;
+    T* cst = taps > 0 ? (T*)m->conv_state + run.canon_off[q] : (T*)nullptr;
+    const T* cwq = taps > 0 ? w(q == 0 ? DN_SQ_CANON1 : DN_SQ_CANON2) : (const T*)nullptr;
     CK(launch(k_read_norm<T>, dim3(N), nthr, nsm, s, m->xs, N, W, S, w(q == 0 ? DN_SQ_HC1_IN : DN_SQ_HC2_IN), w(nrm), dyt ? 0 : 1, 0, c.eps, (const int32_t*)nullptr, dst,
-              w(nb), dyt ? w(na) : (const T*)nullptr, lnorm));
-    if (taps > 0) {
+              w(nb), dyt ? w(na) : (const T*)nullptr, lnorm, fused ? cwq : (const T*)nullptr, taps, b.slot, cst, m->conv_stride));
+    if (taps > 0 && !fused) {
       CK(mark(m, DN_SEQ_PH_CANON, s));
-      T* cst = (T*)m->conv_state + run.canon_off[q];
-      const int fused = b.max_len == 1 ? 1 : 0;      // every entry one token: the kernel carries the row itself
-      CK(launch(k_canon<T>, dim3(N), dim3(W >= 1024 ? 256 : 128), 0, s, (const T*)m->hn, w(q == 0 ? DN_SQ_CANON1 : DN_SQ_CANON2), taps, b, W, cst, m->conv_stride, (T*)m->h, fused));
-      if (!fused && taps > 1) {
+      const int thr = 128, per = thr * (16 / (int)sizeof(T));
+      CK(launch(k_canon<T>, dim3((N + CANON_TOK - 1) / CANON_TOK, (W + per - 1) / per), dim3(thr), 0, s, (const T*)m->hn, cwq, taps, b, W, (const T*)cst, m->conv_stride, (T*)m->h));
+      if (taps > 1) {
         CarrySrc<T> cs{{(const T*)m->hn, nullptr, nullptr}, {W, 0, 0}};
         CK(launch(k_conv_carry<T>, dim3((W + 127) / 128, b.E, 1), dim3(128), 0, s, cs, taps, b, cst, m->conv_stride));
       }
@@ -1207,7 +1209,9 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
       }
       CK(linear<T>(m, s, (const T*)m->lr, l.w[DN_SQ_DECAY2], nullptr, m->dz, N, l.Rc, lc.rank, true, 0, LinMaps{wm(DN_SQ_DECAY2), nullptr, &l.x_lr}));
       PH(DN_SEQ_PH_RECUR_PREP);
-      CK(launch(k_gdelta_prep<T>, dim3(N), dim3(32 * std::min(8, lc.r_heads)), 0, s, lc.r_heads, lc.r_dim, (const T*)m->uq, (const T*)m->uk, (const T*)m->uv,
+      // few tokens: the heads spread over blocks of four warps; many: one block of up to eight warps a token
+      const int gw = std::min(N <= 64 ? 4 : 8, lc.r_heads);
+      CK(launch(k_gdelta_prep<T>, dim3(N, N <= 64 ? (lc.r_heads + gw - 1) / gw : 1), dim3(32 * gw), 0, s, lc.r_heads, lc.r_dim, (const T*)m->uq, (const T*)m->uk, (const T*)m->uv,
                 w(DN_SQ_DECAY_B), w(DN_SQ_R_AB), m->qn, m->kn, m->vv, m->dz, m->un, m->aun));
       PH(DN_SEQ_PH_RECUR);
       {
@@ -1303,7 +1307,8 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
   if (n_want > 0) {
     PH(DN_SEQ_PH_NORM);
     CK(launch(k_read_norm<T>, dim3(n_want), nthr, nsm, s, m->xs, N, W, S, (const T*)nullptr, (const T*)m->final_norm, dyt ? 0 : 1, 1, c.eps, want_dev, (T*)m->h,
-              mwp(DN_SQ_FINAL_NORM_B), dyt ? mwp(DN_SQ_FINAL_NORM_ALPHA) : (const T*)nullptr, lnorm));
+              mwp(DN_SQ_FINAL_NORM_B), dyt ? mwp(DN_SQ_FINAL_NORM_ALPHA) : (const T*)nullptr, lnorm, (const T*)nullptr, 0, (const int32_t*)nullptr, (T*)nullptr,
+              (size_t)0));
     PH(DN_SEQ_PH_HEAD);
     CK(linear<T>(m, s, (const T*)m->h, m->head, nullptr, logits, n_want, c.vocab, W, true, 0, LinMaps{m->tm_head_ok ? &m->tm_head : nullptr, nullptr, &m->x_h}));
     if (c.logit_softcap > 0.f)

@@ -12,7 +12,7 @@
 
 namespace dnseq {
 
-// between the projections and the recurrence, one block per token.  In: r, k, v [N, C] (storage type); zw [N, C] the
+// between the projections and the recurrence; grid (tokens, groups of heads), one warp a head.  In: r, k, v [N, C] (storage type); zw [N, C] the
 // decay's pre-activation and za [N, C] the removal rate's (fp32 products, biases not yet added).  Out, all fp32:
 // rn = r, kn = k, vv = v, zw <- w = exp(-exp(-1/2) sigmoid(zw + w0)), un = u, za <- a * u with a = sigmoid(za + ab).
 // One warp a head for the unit norm: lanes over the head's dims in ascending order, then the lanes pairwise.
@@ -23,7 +23,7 @@ __global__ void k_gdelta_prep(int H, int dk, const T* __restrict__ Ur, const T* 
   const int n = blockIdx.x, C = H * dk;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   const float dmax = 0.6065306597126334f;      // exp(-1/2)
-  for (int h = warp; h < H; h += nw) {
+  for (int h = blockIdx.y * nw + warp; h < H; h += gridDim.y * nw) {
     const size_t base = (size_t)n * C + (size_t)h * dk;
     float ss = 0.f;
     for (int d = lane; d < dk; d += 32) { const float k = ldf(Uk + base + d); ss += k * k; }

@@ -45,6 +45,30 @@ template <> __device__ __forceinline__ float ldf<bf16>(const bf16* p) { return _
 template <class T> __device__ __forceinline__ void stf(T* p, float v);
 template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
 template <> __device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+// v as the storage type holds it
+template <class T> __device__ __forceinline__ float round_to(float v);
+template <> __device__ __forceinline__ float round_to<float>(float v) { return v; }
+template <> __device__ __forceinline__ float round_to<bf16>(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+// 16 bytes of the storage type (8 bf16 or 4 floats) from / to a 16-byte aligned address, as floats
+template <class T> struct Vec16 { static constexpr int n = 16 / sizeof(T); };      // elements of 16 bytes
+__device__ __forceinline__ void ldv(const float* p, float* o) {
+  const float4 v = *reinterpret_cast<const float4*>(p);
+  o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+}
+__device__ __forceinline__ void ldv(const bf16* p, float* o) {
+  const uint4 v = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; i++) { const float2 f = __bfloat1622float2(h[i]); o[2 * i] = f.x; o[2 * i + 1] = f.y; }
+}
+__device__ __forceinline__ void stv(float* p, const float* o) { *reinterpret_cast<float4*>(p) = make_float4(o[0], o[1], o[2], o[3]); }
+__device__ __forceinline__ void stv(bf16* p, const float* o) {
+  uint4 v;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; i++) h[i] = __floats2bfloat162_rn(o[2 * i], o[2 * i + 1]);
+  *reinterpret_cast<uint4*>(p) = v;
+}
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
@@ -144,13 +168,51 @@ __global__ void k_embed(const T* __restrict__ embed, Batch b, float scale, int W
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// the sublayers' input convolution, for V = 16 bytes of adjacent columns a thread: the V x TAPS weights of the columns
+// c .. c + V - 1 are TAPS adjacent 16-byte vectors of cw [W, TAPS]; wl[i * TAPS + j] is column c + i, tap j
+#define DN_TAPS_SWITCH(taps, CALL) \
+  switch (taps) { case 1: { CALL(1); } break; case 2: { CALL(2); } break; case 3: { CALL(3); } break; case 4: { CALL(4); } break; case 5: { CALL(5); } break; \
+                  case 6: { CALL(6); } break; case 7: { CALL(7); } break; case 8: { CALL(8); } break; default: { CALL(9); } break; }
+template <class T, int TAPS>
+__device__ __forceinline__ void canon_weights(const T* __restrict__ cw, int c, float* wl) {
+  constexpr int V = Vec16<T>::n;
+#pragma unroll
+  for (int jj = 0; jj < TAPS; jj++) ldv(cw + (size_t)c * TAPS + jj * V, wl + jj * V);
+}
+// one token whose older rows are all carried rows st[0 .. TAPS - 2] (st[TAPS - 2] the newest): u is the token's normed row
+// in shared memory; writes h = u + conv and moves the row into the carried ones.  Taps in ascending order, the token's own last.
+template <class T, int TAPS>
+__device__ __forceinline__ void canon_tail(const float* __restrict__ u, const T* __restrict__ cw, T* __restrict__ st, T* __restrict__ hrow, int W) {
+  constexpr int V = Vec16<T>::n;
+  for (int c = threadIdx.x * V; c < W; c += blockDim.x * V) {
+    float wl[V * TAPS], a[V], x[V];
+    canon_weights<T, TAPS>(cw, c, wl);
+#pragma unroll
+    for (int i = 0; i < V; i++) a[i] = 0.f;
+#pragma unroll
+    for (int j = 0; j + 1 < TAPS; j++) {
+      ldv(st + (size_t)j * W + c, x);
+#pragma unroll
+      for (int i = 0; i < V; i++) a[i] += wl[i * TAPS + j] * x[i];
+      if (j > 0) stv(st + (size_t)(j - 1) * W + c, x);      // row j moves to j - 1
+    }
+#pragma unroll
+    for (int i = 0; i < V; i++) { x[i] = u[c + i]; a[i] = x[i] + (a[i] + wl[i * TAPS + TAPS - 1] * x[i]); }
+    stv(hrow + c, a);
+    if (TAPS > 1) stv(st + (size_t)(TAPS - 2) * W + c, x);
+  }
+}
+
 // stream read-out (u = sum_s in[s] x_s, or x_0) + RMS norm with weight (1 + w) or w; rows[] optionally gathers.
 // 16-byte loads of the streams when the width allows; a thread's partial sum of squares runs over its own columns in
 // ascending order and the block adds the partials by index, so the result depends on W and the block size only.
 template <class T>
 __global__ void k_read_norm(const float* __restrict__ xs, int N, int W, int S, const T* __restrict__ hc_in, const T* __restrict__ nw,
                             int one_plus, int sum_all, float eps, const int32_t* __restrict__ rows, T* __restrict__ h,
-                            const T* __restrict__ nb, const T* __restrict__ nalpha, int layer_norm) {
+                            const T* __restrict__ nb, const T* __restrict__ nalpha, int layer_norm,
+                            const T* __restrict__ cw = nullptr, int taps = 0, const int32_t* __restrict__ slot_of = nullptr,
+                            T* __restrict__ cstate = nullptr, size_t slot_stride = 0) {
   extern __shared__ __align__(16) float sm[];
   float* u = sm;            // [W]
   float* red = sm + W;      // [33]
@@ -191,14 +253,45 @@ __global__ void k_read_norm(const float* __restrict__ xs, int N, int W, int S, c
     float sd = 0.f;
     for (int c = threadIdx.x; c < W; c += blockDim.x) { const float d = u[c] - mean; sd += d * d; }
     const float rinv = 1.f / sqrtf(block_sum(sd, red) / (float)W + eps);
-    for (int c = threadIdx.x; c < W; c += blockDim.x) stf(h + (size_t)r * W + c, (u[c] - mean) * rinv * ldf(nw + c) + ldf(nb + c));
-    return;
+    if (cw) {
+      for (int c = threadIdx.x; c < W; c += blockDim.x) u[c] = round_to<T>((u[c] - mean) * rinv * ldf(nw + c) + ldf(nb + c));
+    } else {
+      for (int c = threadIdx.x; c < W; c += blockDim.x) stf(h + (size_t)r * W + c, (u[c] - mean) * rinv * ldf(nw + c) + ldf(nb + c));
+      return;
+    }
+  } else {
+    ss = block_sum(ss, red);
+    const float rinv = 1.f / sqrtf(ss / (float)W + eps);
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+      const float g = ldf(nw + c) + (one_plus ? 1.f : 0.f);
+      if (cw) u[c] = round_to<T>(u[c] * rinv * g);
+      else stf(h + (size_t)r * W + c, u[c] * rinv * g);
+    }
+    if (!cw) return;
   }
-  ss = block_sum(ss, red);
-  const float rinv = 1.f / sqrtf(ss / (float)W + eps);
-  for (int c = threadIdx.x; c < W; c += blockDim.x) {
-    const float g = ldf(nw + c) + (one_plus ? 1.f : 0.f);
-    stf(h + (size_t)r * W + c, u[c] * rinv * g);
+  // cw != null (steps whose entries bring one token each): the sublayer's input convolution in the same pass.  u holds the
+  // normed row as the storage type rounds it; older rows come from the slot's carried rows st[0 .. taps - 2] (st[taps - 2] the
+  // newest), which then take the row in.  Taps in ascending order, the token's own last, as k_canon.
+  __syncthreads();
+  T* st = cstate + (size_t)slot_of[n] * slot_stride;
+  constexpr int V = Vec16<T>::n;
+  if (W % V == 0 && ((((uintptr_t)st | (uintptr_t)cw) & 15) == 0)) {
+#define DN_CALL(K) canon_tail<T, K>(u, cw, st, h + (size_t)r * W, W)
+    DN_TAPS_SWITCH(taps, DN_CALL)
+#undef DN_CALL
+  } else {
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+      const float v = u[c];
+      float a = 0.f;
+      for (int j = 0; j + 1 < taps; j++) {
+        const float x = ldf(st + (size_t)j * W + c);
+        a += ldf(cw + (size_t)c * taps + j) * x;
+        if (j > 0) stf(st + (size_t)(j - 1) * W + c, x);
+      }
+      a += ldf(cw + (size_t)c * taps + taps - 1) * v;
+      stf(h + (size_t)r * W + c, v + a);
+      if (taps > 1) stf(st + (size_t)(taps - 2) * W + c, v);
+    }
   }
 }
 
@@ -365,14 +458,29 @@ __global__ void k_rms2_join(float* __restrict__ x, int W, const float* __restric
   __shared__ float red[33];
   const size_t base = (size_t)blockIdx.x * W;
   float s1 = 0.f, s2 = 0.f;
-  for (int c = threadIdx.x; c < W; c += blockDim.x) {
-    const float u = y[base + c], v = y2[base + c];
-    s1 += u * u;
-    s2 += v * v;
-  }
+  // a thread's partial sums run over its own columns in ascending order, four adjacent ones at a time when the width allows
+  const int V = (W & 3) == 0 ? 4 : 1;
+  for (int c = threadIdx.x * V; c < W; c += blockDim.x * V)
+    for (int i = 0; i < V; i++) {
+      const float u = y[base + c + i], v = y2[base + c + i];
+      s1 += u * u;
+      s2 += v * v;
+    }
   s1 = block_sum(s1, red);
   s2 = block_sum(s2, red);
   const float r1 = a / sqrtf(s1 / (float)W + eps), r2 = b / sqrtf(s2 / (float)W + eps);
+  if (V == 4) {
+    for (int c = threadIdx.x * 4; c < W; c += blockDim.x * 4) {
+      const float4 u = *reinterpret_cast<const float4*>(y + base + c), v = *reinterpret_cast<const float4*>(y2 + base + c);
+      float4 o = *reinterpret_cast<float4*>(x + base + c);
+      o.x += u.x * r1 * ldf(w1 + c) + v.x * r2 * ldf(w2 + c);
+      o.y += u.y * r1 * ldf(w1 + c + 1) + v.y * r2 * ldf(w2 + c + 1);
+      o.z += u.z * r1 * ldf(w1 + c + 2) + v.z * r2 * ldf(w2 + c + 2);
+      o.w += u.w * r1 * ldf(w1 + c + 3) + v.w * r2 * ldf(w2 + c + 3);
+      *reinterpret_cast<float4*>(x + base + c) = o;
+    }
+    return;
+  }
   for (int c = threadIdx.x; c < W; c += blockDim.x)
     x[base + c] += y[base + c] * r1 * ldf(w1 + c) + y2[base + c] * r2 * ldf(w2 + c);
 }
@@ -466,7 +574,6 @@ __global__ void __launch_bounds__(256) k_linear(const T* __restrict__ X, const T
 // Y[N, O] = X[N, K] W[O, K]^T for a few rows (N <= 8: decode steps): one warp per output feature streams its weight
 // row once (16-byte loads when the row allows) against all N activations; lane partials in ascending k, one
 // shuffle reduction.  The weights are read exactly once: HBM-bound.
-template <class T> struct Vec16 { static constexpr int n = 16 / sizeof(T); };
 // one warp, one output feature o of one product
 template <class T>
 __device__ __forceinline__ void linear_row(const T* __restrict__ X, const T* __restrict__ Wt, const T* __restrict__ W2, void* __restrict__ Y,
@@ -598,21 +705,55 @@ __global__ void k_conv_carry(CarrySrc<T> src, int taps, Batch b, T* __restrict__
 }
 
 // A sublayer's input passes a causal convolution over time: h[n] = hn[n] + sum_j w[:, j] hn[n - taps + 1 + j], rows
-// before the entry's first one from the slot's carried rows (zeros in a fresh slot).  One block per token.
-// carry != 0 (steps in which every entry brings one token): the token's row also becomes the newest carried row;
-// larger steps run k_conv_carry afterwards.  A thread reads and writes its own columns only.
+// before the entry's first one from the slot's carried rows (zeros in a fresh slot); taps in ascending order.  Grid
+// (groups of CANON_TOK tokens, column groups); a thread takes 16 bytes of columns when the width allows, keeps their
+// weights in registers and walks the group's tokens.  k_conv_carry afterwards makes the step's last rows the carried
+// ones.  (Steps whose entries bring one token each run the convolution inside k_read_norm.)
+constexpr int CANON_TOK = 8;
+template <class T, int TAPS>
+__device__ __forceinline__ void canon_tokens(const T* __restrict__ hn, const T* __restrict__ cw, const Batch& b, int W, const T* __restrict__ state,
+                                             size_t slot_stride, T* __restrict__ h, int n0, int n1, int c) {
+  constexpr int V = Vec16<T>::n;
+  float wl[V * TAPS];
+  canon_weights<T, TAPS>(cw, c, wl);
+  for (int n = n0; n < n1; n++) {
+    const int local = n - b.first[n];
+    const T* st = state + (size_t)b.slot[n] * slot_stride;
+    float a[V], x[V];
+#pragma unroll
+    for (int i = 0; i < V; i++) a[i] = 0.f;
+#pragma unroll
+    for (int j = 0; j < TAPS; j++) {
+      const int back = TAPS - 1 - j;
+      ldv(back <= local ? hn + (size_t)(n - back) * W + c : st + (size_t)(TAPS - 1 - (back - local)) * W + c, x);
+#pragma unroll
+      for (int i = 0; i < V; i++) a[i] += wl[i * TAPS + j] * x[i];
+    }
+#pragma unroll
+    for (int i = 0; i < V; i++) a[i] = x[i] + a[i];      // x: the token's own row (the last tap)
+    stv(h + (size_t)n * W + c, a);
+  }
+}
 template <class T>
-__global__ void k_canon(const T* __restrict__ hn, const T* __restrict__ cw, int taps, Batch b, int W, T* __restrict__ state, size_t slot_stride,
-                        T* __restrict__ h, int carry) {
-  const int n = blockIdx.x, local = n - b.first[n];
-  T* st = state + (size_t)b.slot[n] * slot_stride;
-  for (int c = threadIdx.x; c < W; c += blockDim.x) {
-    float a = 0.f;
-    for (int j = 0; j < taps; j++) a += ldf(cw + (size_t)c * taps + j) * conv_in(hn, W, c, n, local, taps - 1 - j, (const T*)st, W, taps);
-    stf(h + (size_t)n * W + c, ldf(hn + (size_t)n * W + c) + a);
-    if (carry) {
-      for (int j = 0; j + 2 < taps; j++) st[(size_t)j * W + c] = st[(size_t)(j + 1) * W + c];
-      if (taps > 1) st[(size_t)(taps - 2) * W + c] = hn[(size_t)n * W + c];
+__global__ void k_canon(const T* __restrict__ hn, const T* __restrict__ cw, int taps, Batch b, int W, const T* __restrict__ state,
+                        size_t slot_stride, T* __restrict__ h) {
+  const int n0 = blockIdx.x * CANON_TOK, n1 = min(b.N, n0 + CANON_TOK);
+  constexpr int V = Vec16<T>::n;
+  if (W % V == 0 && slot_stride % V == 0 && ((((uintptr_t)state | (uintptr_t)cw) & 15) == 0)) {
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * V;
+    if (c >= W) return;
+#define DN_CALL(K) canon_tokens<T, K>(hn, cw, b, W, state, slot_stride, h, n0, n1, c)
+    DN_TAPS_SWITCH(taps, DN_CALL)
+#undef DN_CALL
+    return;
+  }
+  for (int n = n0; n < n1; n++) {
+    const int local = n - b.first[n];
+    const T* st = state + (size_t)b.slot[n] * slot_stride;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < W; c += gridDim.y * blockDim.x) {
+      float a = 0.f;
+      for (int j = 0; j < taps; j++) a += ldf(cw + (size_t)c * taps + j) * conv_in(hn, W, c, n, local, taps - 1 - j, st, W, taps);
+      stf(h + (size_t)n * W + c, ldf(hn + (size_t)n * W + c) + a);
     }
   }
 }
@@ -843,22 +984,22 @@ __global__ void __launch_bounds__(AT_WARPS * 32) k_attn(Batch b, const T* __rest
   float m = -INFINITY, l = 0.f, acc[MAXV];
 #pragma unroll
   for (int i = 0; i < MAXV; i++) acc[i] = 0.f;
-  // the row of virtual key v in the key (value) pools
-  auto key_row = [&](int v) -> const T* {
-    if (v < nb) return (const T*)ex.pk + pooled_row(bt, v, ex.pool) * Ck;
+  // virtual key v (pooled blocks first, then the tokens lo .. p) lives in row row_of(v) of the token pools, or, with bit 31
+  // set, of the pooled pools; a lane finds its own key's row once and the value loop takes the rows from the lanes
+  auto row_of = [&](int v) -> uint32_t {
+    if (v < nb) return 0x80000000u | (uint32_t)pooled_row(bt, v, ex.pool);
     const int j = lo + v - nb;
-    return kpool + ((size_t)bt[j / PAGE] * PAGE + (j % PAGE)) * Ck;
+    return (uint32_t)bt[j / PAGE] * PAGE + (uint32_t)(j % PAGE);
   };
-  auto val_row = [&](int v) -> const T* {
-    if (v < nb) return (const T*)ex.pv + pooled_row(bt, v, ex.pool) * Cv;
-    const int j = lo + v - nb;
-    return vpool + ((size_t)bt[j / PAGE] * PAGE + (j % PAGE)) * Cv;
-  };
+  const T* kpl = (const T*)ex.pk;
+  const T* vpl = (const T*)ex.pv;
   for (int j0 = (z * AT_WARPS + warp) * 32; j0 < nkeys; j0 += nz * AT_WARPS * 32) {
     const int j = j0 + lane;
     float s = -INFINITY;
+    uint32_t myrow = 0;
     if (j < nkeys) {
-      const T* kr = key_row(j) + g * dk;
+      myrow = row_of(j);
+      const T* kr = ((myrow >> 31) ? kpl : kpool) + (size_t)(myrow & 0x7fffffffu) * Ck + g * dk;
       float d0 = 0.f;
       if (kvec) {
 #pragma unroll 8
@@ -881,10 +1022,11 @@ __global__ void __launch_bounds__(AT_WARPS * 32) k_attn(Batch b, const T* __rest
 #pragma unroll
     for (int i = 0; i < MAXV; i++) acc[i] *= corr;
     const int cnt = min(32, nkeys - j0);
-#pragma unroll 4
+#pragma unroll 8
     for (int t = 0; t < cnt; t++) {
       const float pt = __shfl_sync(0xffffffffu, pj, t);
-      const T* vr = val_row(j0 + t) + g * dv + lane * VPL;
+      const uint32_t rw = __shfl_sync(0xffffffffu, myrow, t);
+      const T* vr = ((rw >> 31) ? vpl : vpool) + (size_t)(rw & 0x7fffffffu) * Cv + g * dv + lane * VPL;
 #pragma unroll
       for (int i0 = 0; i0 < MAXV; i0 += 8) {
         if (i0 < vcnt) {

@@ -331,3 +331,114 @@ def test_token_loop_schedules_decodes_beside_prompt_portions(monkeypatch):
     assert all(sum(s) <= 16 for s in m.steps)
     assert any(len(s) == 2 and 1 in s and max(s) > 1 for s in m.steps)      # a decode token beside a prompt portion
     assert m.free_slots == 2 and m.free_pages == 6                             # everything was handed back
+
+
+def _vulanex_cfg():
+    rot = {"base": 777.0, "dims": 6, "scaling": {"factor": 4.0, "original": 32, "fast": 2.0, "slow": 0.5}}
+    left = {"heads": 4, "kv_heads": 2, "dim": 10, "vdim": 7, "scale": 0.3, "mask": {"size": 9, "pool": 4}, "rot": rot}
+    att = {"heads": 6, "kv_heads": 3, "dim": 5, "vdim": 5, "scale": 0.4, "q_temp": {"coef": 0.25, "every": 16}}
+    return {"architecture": "Vulanex", "vocab": 50, "width": 32, "norm": {"eps": 1e-5}, "logit_scale": 0.75, "canon": {"taps": 3},
+            "embedding": {"bigram": {"buckets": 11, "mul_prev": 5, "mul_cur": 3}},
+            "layers": [{"type": "parallel", "mixer": {"left": left, "right": {"heads": 3, "dim": 6}}, "mlp": {"kind": "dense", "ff": 40}},
+                       {"type": "attention", "mixer": att, "mlp": None},
+                       {"type": "parallel", "mixer": {"left": {**left, "mask": None, "rot": None}, "right": {"heads": 1, "dim": 12}}, "mlp": None},
+                       {"type": "attention", "mixer": {k: v for k, v in att.items() if k != "q_temp"}, "mlp": {"kind": "dense", "ff": 24}}]}
+
+
+def test_vulanex_config_and_checkpoint_names():
+    """every constant of the config lands in the structs, what the design fixes comes from the family, the decay's inner
+    size comes from a tensor's shape, and every tensor the oracle writes finds its place through the aliases"""
+    from dnet_b200 import _seqabi
+    from dnet_b200.core.models import ring_model_class
+    from dnet_b200.core.models.seqmix import _LAYER_KEY, parse_layer_list
+    from oracle import vulanex_oracle as vo
+
+    cfg = _vulanex_cfg()
+    cls = ring_model_class("vulanex")
+    shapes = vo.tensor_shapes(cfg, rank=5)
+    with pytest.raises(ValueError):
+        parse_layer_list(cfg, cls.family, None)              # the decay's inner size is in no config key
+    sc, layers = parse_layer_list(cfg, cls.family, shapes)
+    assert (sc.norm_kind, sc.post_norm, sc.no_pre_norm, sc.embed_norm, sc.streams) == (_seqabi.DN_NORM_LAYER, 0, 0, 0, 0)
+    assert (sc.canon_taps, sc.bigram_buckets, sc.bigram_mul_prev, sc.bigram_mul_cur) == (3, 11, 5, 3)
+    assert abs(sc.logit_scale - 0.75) < 1e-7 and abs(sc.eps - 1e-5) < 1e-9 and abs(sc.embed_scale - 1.0) < 1e-7
+    assert [l.mixer for l in layers] == [_seqabi.DN_MIX_PARALLEL, _seqabi.DN_MIX_ATTENTION] * 2
+    p0, a1, p2, a3 = layers
+    assert (p0.heads, p0.kv_heads, p0.dim, p0.vdim, p0.chunk, p0.pool, p0.mask_kind) == (4, 2, 10, 7, 9, 4, _seqabi.DN_MASK_WINDOW)
+    assert (p0.rot_dims, p0.rot_layout, p0.qk_norm, p0.sink, p0.v_is_k) == (6, _seqabi.DN_ROT_HALF, _seqabi.DN_QKNORM_HEAD, 1, 0)
+    assert (p0.yarn_factor, p0.yarn_original, p0.yarn_fast, p0.yarn_slow) == (4.0, 32.0, 2.0, 0.5) and abs(p0.rot_base - 777.0) < 1e-3
+    assert (p0.r_kind, p0.r_heads, p0.r_dim, p0.r_vdim, p0.rank, p0.branch_norm) == (_seqabi.DN_RIGHT_GDELTA, 3, 6, 6, 5, 1)
+    assert p0.left_scale == 0.5 and p0.right_scale == 0.5 and p0.ff == 40 and p0.qtemp_every == 0
+    assert (p2.chunk, p2.pool, p2.rot_dims, p2.yarn_factor, p2.r_heads, p2.r_dim, p2.ff) == (0, 0, 0, 0.0, 1, 12, 0)
+    assert (a1.heads, a1.kv_heads, a1.dim, a1.vdim, a1.v_is_k, a1.qk_norm, a1.sink, a1.rot_dims, a1.chunk, a1.pool) == (6, 3, 5, 5, 1, 0, 0, 0, 0, 0)
+    assert abs(a1.qtemp_coef - 0.25) < 1e-7 and a1.qtemp_every == 16 and abs(a1.scale - 0.4) < 1e-7 and a1.ff == 0
+    assert a3.qtemp_every == 0 and a3.ff == 24
+    m = cls.__new__(cls)
+    m.config, m._cfg_struct, m._layer_structs, m.hidden_size, m.vocab_size = cfg, sc, layers, sc.width, sc.vocab
+    want = m.expected_tensors()
+    assert "head" not in want and "l1.mix.v" not in want      # the embedding table is the head; the values are the keys
+    assert "l1.canon2" not in want and "l0.canon2" in want    # no feed-forward, no convolution before it
+    got = {}
+    for key, sh in shapes.items():
+        if _LAYER_KEY.match(key):
+            lname, suffix = key.split(".", 1)
+            kind = cfg["layers"][int(lname[1:])]["type"]
+            suffix = cls.tensor_alias.get(kind, {}).get(suffix, cls.tensor_alias.get("*", {}).get(suffix, suffix))
+            key = f"{lname}.{suffix}"
+        got[key] = tuple(sh)
+    assert got == {k: tuple(v) for k, v in want.items()}
+    for k in want:
+        if _LAYER_KEY.match(k):
+            assert k.split(".", 1)[1] in _seqabi.LAYER_SLOT, k
+
+
+def test_vulanex_oracle_by_hand():
+    """the oracle's pieces on numbers small enough to follow"""
+    from oracle import vulanex_oracle as vo
+
+    D = torch.float64
+    # bigram rows: the extra row for the first token, then the hash of (previous, current)
+    assert vo.bigram_rows([4, 9, 4], 11, 5, 3) == [11, (4 * 5 + 9 * 3) % 11, (9 * 5 + 4 * 3) % 11]
+    # the convolution: tap taps - 1 meets the token itself, tap 0 the oldest, zeros before the sequence
+    h = torch.tensor([[1.0], [10.0], [100.0]], dtype=D)
+    cw = torch.tensor([[0.5, 2.0, 3.0]], dtype=D)
+    assert torch.allclose(vo.input_convolution(h, cw)[:, 0], torch.tensor([1 + 3.0, 10 + 2.0 + 30.0, 100 + 0.5 + 20.0 + 300.0], dtype=D))
+    # the query's factor steps up where floor((p + 1) / every) does
+    f = vo.query_temperature(9, 2.0, 4)
+    assert f[:3].tolist() == [1.0] * 3 and abs(float(f[3]) - (1 + 2 * math.log(2))) < 1e-12 and abs(float(f[7]) - (1 + 2 * math.log(3))) < 1e-12
+    # visibility: a window of 3 with blocks of 2: position 6 sees tokens 4, 5, 6 and the blocks that end at or before 3
+    assert vo.visible(6, 3, 2) == ([4, 5, 6], [0, 1]) and vo.visible(5, 3, 2) == ([3, 4, 5], [0]) and vo.visible(2, 3, 2) == ([0, 1, 2], [])
+    assert vo.visible(4, 0, 0) == ([0, 1, 2, 3, 4], []) and vo.visible(4, 2, 0) == ([3, 4], [])
+    # a block's key and value are means; a sink as large as the only score halves the only key's weight
+    q = torch.zeros(3, 1, 1, dtype=D)
+    k = torch.zeros(3, 1, 1, dtype=D)
+    v = torch.tensor([[[2.0]], [[6.0]], [[100.0]]], dtype=D)
+    o = vo.softmax_attention(q, k, v, 1.0, size=1, pool=2)          # position 2: itself and block 0 (mean value 4), equal scores
+    assert abs(float(o[2, 0, 0]) - 52.0) < 1e-12 and float(o[1, 0, 0]) == 6.0
+    o = vo.softmax_attention(q[:1], k[:1], v[:1], 1.0, sink=torch.tensor([0.0], dtype=D))
+    assert abs(float(o[0, 0, 0]) - 1.0) < 1e-12
+    # frequencies: without scaling base^(-2i/dims); with it fast pairs keep theirs, slow ones are divided by the factor
+    f, m = vo.rotary_frequencies({"base": 100.0, "dims": 4})
+    assert torch.allclose(f, torch.tensor([1.0, 0.1], dtype=D)) and m == 1.0
+    f, m = vo.rotary_frequencies({"base": 10000.0, "dims": 8, "scaling": {"factor": 4.0, "original": 64, "fast": 8.0, "slow": 1.0}})
+    plain = torch.tensor([10000.0 ** (-2 * i / 8) for i in range(4)], dtype=D)
+    assert float(f[0]) == 1.0 and abs(float(f[3]) - float(plain[3]) / 4.0) < 1e-15 and abs(m - (0.1 * math.log(4.0) + 1.0)) < 1e-15
+    assert all(float(plain[i]) / 4.0 - 1e-15 <= float(f[i]) <= float(plain[i]) + 1e-15 for i in range(4))
+    # rotation by halves: dim i pairs with dim i + dims / 2; scores depend on the distance only
+    e0 = torch.tensor([[[1.0, 0.0, 0.0, 0.0, 7.0]]] * 2, dtype=D)
+    r = vo.rotary_half(e0, {"base": 100.0, "dims": 4})
+    assert abs(float(r[1, 0, 2]) - math.sin(1.0)) < 1e-12 and float(r[1, 0, 1]) == 0.0 and float(r[1, 0, 4]) == 7.0 and torch.equal(r[0], e0[0])
+    # the delta rule: no decay (w = 1), full removal (a = 1): an orthonormal key's value is stored and replaced exactly
+    k = torch.eye(4, dtype=D)[[0, 1, 0]][:, None, :]
+    v = torch.tensor([[1.0, 2.0, 0.0, 0.0], [3.0, 4.0, 0.0, 0.0], [5.0, 6.0, 0.0, 0.0]], dtype=D)[:, None, :]
+    one = torch.ones(3, 1, 4, dtype=D)
+    o = vo.generalized_delta_rule(k, k, v, one, one)
+    assert torch.allclose(o, v, atol=1e-5)
+    # no removal (a = 0), decay 1/2: the value written two tokens ago is read back at a quarter beside the new one
+    o = vo.generalized_delta_rule(k, k, v, 0.5 * one, 0.0 * one)
+    assert torch.allclose(o[2, 0], 0.25 * v[0, 0] + v[2, 0], atol=1e-5)
+    # the decay's range: exp(-e^(-1/2) sigmoid(.)) lies between exp(-e^(-1/2)) and 1
+    assert abs(math.exp(-math.exp(-0.5)) - 0.5452) < 1e-3
+    # layer norm with the variance of the deviations
+    x = torch.tensor([[1.0, 3.0]], dtype=D)
+    assert torch.allclose(vo.layer_norm(x, torch.tensor([2.0, 2.0]), torch.tensor([0.5, 0.5]), 0.0), torch.tensor([[-1.5, 2.5]], dtype=D))
