@@ -981,6 +981,9 @@ __global__ void __launch_bounds__(AT_WARPS * 32) k_attn(Batch b, const T* __rest
   const int vcnt = min(VPL, max(0, dv - lane * VPL));
   // 8- or 16-byte value loads: a lane's run of VPL numbers must start on such a boundary in every row
   const bool vvec = (dv % 32) == 0 && ((size_t)Cv * sizeof(T)) % 16 == 0 && ((VPL * sizeof(T)) % 16 == 0 || VPL * sizeof(T) == 8);
+  const int vbytes = VPL * (int)sizeof(T);
+  const bool vraw = (dv % 32) == 0 && (vbytes == 4 || vbytes == 8 || vbytes == 16) && ((size_t)Cv * sizeof(T)) % vbytes == 0 &&
+                    ((((uintptr_t)vpool | (uintptr_t)ex.pv) & 15) == 0);
   float m = -INFINITY, l = 0.f, acc[MAXV];
 #pragma unroll
   for (int i = 0; i < MAXV; i++) acc[i] = 0.f;
@@ -1022,6 +1025,33 @@ __global__ void __launch_bounds__(AT_WARPS * 32) k_attn(Batch b, const T* __rest
 #pragma unroll
     for (int i = 0; i < MAXV; i++) acc[i] *= corr;
     const int cnt = min(32, nkeys - j0);
+    if (vraw) {
+      // a lane's run of values is one 4-, 8- or 16-byte load a row: the loads of eight rows are issued together, then
+      // their sums run in the rows' order (rows beyond the tile repeat its last row with weight zero)
+      for (int t0 = 0; t0 < cnt; t0 += 8) {
+        uint4 raw[8];
+        float pt[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+          const int t = min(t0 + u, cnt - 1);
+          const uint32_t rw = __shfl_sync(0xffffffffu, myrow, t);
+          pt[u] = t0 + u < cnt ? __shfl_sync(0xffffffffu, pj, t) : 0.f;
+          const T* vr = ((rw >> 31) ? vpl : vpool) + (size_t)(rw & 0x7fffffffu) * Cv + g * dv + lane * VPL;
+          if (vbytes == 16) raw[u] = *reinterpret_cast<const uint4*>(vr);
+          else if (vbytes == 8) { const uint2 r2 = *reinterpret_cast<const uint2*>(vr); raw[u] = make_uint4(r2.x, r2.y, 0u, 0u); }
+          else raw[u] = make_uint4(*reinterpret_cast<const uint32_t*>(vr), 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+          const T* e = reinterpret_cast<const T*>(&raw[u]);
+#pragma unroll
+          for (int i = 0; i < 16 / (int)sizeof(T); i++)
+            if (i < MAXV && i < VPL) acc[i] = fmaf(pt[u], ldf(e + i), acc[i]);
+        }
+      }
+      m = mn;
+      continue;
+    }
 #pragma unroll 8
     for (int t = 0; t < cnt; t++) {
       const float pt = __shfl_sync(0xffffffffu, pj, t);
