@@ -1215,17 +1215,31 @@ static int step_T(dn_seq_model* m, const Batch& b, int n_want, const int32_t* wa
                 w(DN_SQ_DECAY_B), w(DN_SQ_R_AB), m->qn, m->kn, m->vv, m->dz, m->un, m->aun));
       PH(DN_SEQ_PH_RECUR);
       {
-        int R, P;
-        recur_shape(lc.r_dim, &R, &P);
-        const int cols = P >= 2 ? 16 : 32, dv = lc.r_dim;
+        // rows a lane (R), lanes a column (P), columns a block.  The token loop is bound by the latency of its dependent
+        // instructions, so a model with few heads (fewer blocks of 16 columns than the GPU has SMs) takes 4 rows a lane and 8
+        // columns a block: four times the warps.  A function of the model's sizes only: the order of the sums does not
+        // depend on the batch.
+        static const int RPC[9][4] = {{4, 4, 1, 32}, {8, 4, 2, 16}, {16, 4, 4, 8}, {32, 4, 8, 8}, {64, 4, 16, 8}, {128, 8, 16, 8}, {256, 8, 32, 8},
+                                      {512, 16, 32, 8}, {1024, 32, 32, 8}};
+        int R = 32, P = 32, cols = 8;
+        if (lc.r_heads * ((lc.r_dim + 15) / 16) < 148) {
+          for (int i = 8; i >= 0; i--) if (lc.r_dim <= RPC[i][0]) { R = RPC[i][1]; P = RPC[i][2]; cols = RPC[i][3]; }
+        } else {
+          recur_shape(lc.r_dim, &R, &P);
+          cols = P >= 2 ? 16 : 32;
+        }
+        const int dv = lc.r_dim;
         dim3 grid(b.E * lc.r_heads, (dv + cols - 1) / cols);
-        const int per = 5 * P * (R + 4) + cols;
+        const int per = 5 * P * (R == 4 ? 4 : R + 4) + cols;
         const int TB = std::max(1, std::min(16, 5800 / per));      // two tiles within ~46 KB of shared memory
         const size_t dsm = (size_t)2 * TB * per * 4;
 #define GD(Rv_, Pv_, Cv_) if (R == Rv_ && P == Pv_) CK(launch(k_gdelta_rule<Rv_, Pv_, Cv_>, grid, dim3(Cv_ * Pv_), dsm, s, b, lc.r_heads, lc.r_dim, dv, TB, \
                            (const float*)m->qn, (const float*)m->kn, (const float*)m->vv, (const float*)m->dz, (const float*)m->un, (const float*)m->aun, st, \
                            m->delta_stride, m->od))
-        GD(8, 1, 32); GD(8, 2, 16); GD(8, 4, 16); GD(8, 8, 16); GD(16, 8, 16); GD(16, 16, 16); GD(16, 32, 16); GD(32, 32, 16);
+#define GD2(Rv_, Pv_, Cv_) if (cols == Cv_) GD(Rv_, Pv_, Cv_)
+        GD(4, 1, 32); GD(4, 2, 16); GD(4, 4, 8); GD(4, 8, 8); GD(4, 16, 8); GD(8, 16, 8); GD(8, 32, 8); GD2(16, 32, 8); GD2(32, 32, 8);
+        GD(8, 1, 32); GD(8, 2, 16); GD(8, 4, 16); GD(8, 8, 16); GD(16, 8, 16); GD(16, 16, 16); GD2(16, 32, 16); GD2(32, 32, 16);
+#undef GD2
 #undef GD
       }
       PH(DN_SEQ_PH_RECUR_OUT);

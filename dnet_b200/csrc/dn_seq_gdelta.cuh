@@ -46,8 +46,8 @@ __global__ void k_gdelta_prep(int H, int dk, const T* __restrict__ Ur, const T* 
 // The recurrence, token by token.  A block owns COLS columns of one (entry, head); P adjacent lanes share a column, each
 // holding R consecutive rows (P R >= dk) in registers.  State [slot][head][dk][dv] fp32, read once and written once per
 // step.  A token's u, a * u, w, k, r and the block's COLS values come through shared memory in tiles of TB tokens, copied
-// asynchronously one tile ahead; each vector lies there as P runs of R values padded by 4 floats (the 16-byte reads of
-// a column's P lanes fall into different banks); rows from dk up are zero.  The sums u . s and s . r run over a
+// asynchronously one tile ahead; each vector lies there as P runs of R values, padded by 4 floats where R > 4 (the 16-byte
+// reads of a column's P lanes fall into different banks); rows from dk up are zero.  The sums u . s and s . r run over a
 // thread's rows in four interleaved partial sums, then over the lanes of a column pairwise: an order fixed by (dk, P),
 // whatever the tile size or the cut of a prompt.  The read-out of token t is reduced over the lanes together with
 // u . s of token t + 1 (two independent shuffle chains in flight).
@@ -59,7 +59,8 @@ __global__ void __launch_bounds__(COLS * P) k_gdelta_rule(Batch b, int H, int dk
                                                           float* __restrict__ o) {
   static_assert(COLS * P >= 32 && (COLS * P) % 32 == 0 && COLS <= 32, "whole warps");
   extern __shared__ __align__(16) float dsm[];      // 2 x TB x per
-  constexpr int KP = P * (R + 4);
+  constexpr int RS = R == 4 ? 4 : R + 4;            // a lane's run with its padding (none for runs of one 16-byte read)
+  constexpr int KP = P * RS;
   constexpr int per = 5 * KP + COLS;                // u, a u, w, k, r, v[COLS]
   const int e = blockIdx.x / H, h = blockIdx.x % H;
   const int part = threadIdx.x % P, colb = threadIdx.x / P, col = blockIdx.y * COLS + colb;
@@ -80,7 +81,7 @@ __global__ void __launch_bounds__(COLS * P) k_gdelta_rule(Batch b, int H, int dk
       float* dst = dsm + ((size_t)buf * TB + t) * per;
       const size_t base = (size_t)n * C + (size_t)h * dk;
       for (int c = lane; c < P * R; c += 32) {
-        const int idx = (c / R) * (R + 4) + (c % R);
+        const int idx = (c / R) * RS + (c % R);
         if (c < dk) {
           cp_async4(dst + idx, un + base + c); cp_async4(dst + KP + idx, au + base + c); cp_async4(dst + 2 * KP + idx, wd + base + c);
           cp_async4(dst + 3 * KP + idx, kn + base + c); cp_async4(dst + 4 * KP + idx, rn + base + c);
@@ -103,7 +104,7 @@ __global__ void __launch_bounds__(COLS * P) k_gdelta_rule(Batch b, int H, int dk
     __syncthreads();
     const int cnt = min(TB, s1 - n0);
     for (int t = 0; t < cnt; t++) {
-      const float* in = dsm + ((size_t)buf * TB + t) * per + part * (R + 4);
+      const float* in = dsm + ((size_t)buf * TB + t) * per + part * RS;
       const float4* u4 = reinterpret_cast<const float4*>(in);
       const float4* a4 = reinterpret_cast<const float4*>(in + KP);
       const float4* w4 = reinterpret_cast<const float4*>(in + 2 * KP);

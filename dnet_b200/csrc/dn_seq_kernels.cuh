@@ -1003,6 +1003,11 @@ __global__ void __launch_bounds__(AT_WARPS * 32) k_attn(Batch b, const T* __rest
     if (j < nkeys) {
       myrow = row_of(j);
       const T* kr = ((myrow >> 31) ? kpl : kpool) + (size_t)(myrow & 0x7fffffffu) * Ck + g * dk;
+      {   // the key's value row is needed after the scores: ask for its lines now, so that the value loop finds them in L2
+        const char* vrow = reinterpret_cast<const char*>(((myrow >> 31) ? vpl : vpool) + (size_t)(myrow & 0x7fffffffu) * Cv + g * dv);
+        if (vrow != reinterpret_cast<const char*>(kr))
+          for (int o = 0; o < dv * (int)sizeof(T); o += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(vrow + o));
+      }
       float d0 = 0.f;
       if (kvec) {
 #pragma unroll 8
@@ -1182,7 +1187,9 @@ __global__ void __launch_bounds__(128) k_attn_tiles(Batch b, const bf16* __restr
   extern __shared__ __align__(16) unsigned char smraw[];
   bf16* Qs = reinterpret_cast<bf16*>(smraw);
   bf16* Ks = Qs + AT_ROWS * LQ;
-  bf16* Vs = Ks + AT_ROWS * LQ;
+  // values that are the keys (one pool, equal tile shapes): the key tile is the value tile, nothing is staged twice
+  const bool vk = DKP == DVP && dk == dv && vpool == kpool && ex.pv == ex.pk;
+  bf16* Vs = vk ? Ks : Ks + AT_ROWS * LQ;
   // which entry and which of its 64-row tiles
   int e = 0, t = blockIdx.x;
   for (; e < b.E; e++) {
@@ -1223,12 +1230,12 @@ __global__ void __launch_bounds__(128) k_attn_tiles(Batch b, const bf16* __restr
     __syncthreads();
     if (pooled) {
       load_tile64_rows<LQ>(Ks, (const bf16*)ex.pk + (size_t)g * dk, (size_t)Ck, dk, min(AT_ROWS, nb_last - j0), bt, j0, ex.pool);
-      load_tile64_rows<LV>(Vs, (const bf16*)ex.pv + (size_t)g * dv, (size_t)Cv, dv, min(AT_ROWS, nb_last - j0), bt, j0, ex.pool);
+      if (!vk) load_tile64_rows<LV>(Vs, (const bf16*)ex.pv + (size_t)g * dv, (size_t)Cv, dv, min(AT_ROWS, nb_last - j0), bt, j0, ex.pool);
     } else {
       const size_t prow = (size_t)bt[j0 / PAGE] * PAGE;
       const int kvalid = min(PAGE, p_last - j0 + 1);      // rows of the page beyond the last query's position are not read
       load_tile64<LQ>(Ks, kpool + prow * Ck + (size_t)g * dk, (size_t)Ck, dk, kvalid);
-      load_tile64<LV>(Vs, vpool + prow * Cv + (size_t)g * dv, (size_t)Cv, dv, kvalid);
+      if (!vk) load_tile64<LV>(Vs, vpool + prow * Cv + (size_t)g * dv, (size_t)Cv, dv, kvalid);
     }
     __syncthreads();
     if (!warp_live) continue;

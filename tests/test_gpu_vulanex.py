@@ -138,6 +138,10 @@ MECHANISMS = {
     "parallel_large_heads": bare([par(heads=2, kv_heads=1, dim=128, vdim=128, scale=0.1, right={"heads": 1, "dim": 128})], width=64),
     "delta_rule_wide": bare([par(right={"heads": 1, "dim": 160})]),
     "delta_rule_many_small_heads": bare([par(right={"heads": 11, "dim": 4})]),
+    # as many (head, 16 columns) pairs as the GPU has SMs and more: the recurrence then takes more rows a lane and 16 columns a block
+    "delta_rule_150_heads": bare([par(right={"heads": 150, "dim": 8})]),
+    "delta_rule_40_heads_of_64": bare([par(right={"heads": 40, "dim": 64})]),
+    "delta_rule_19_heads_of_128": bare([par(right={"heads": 19, "dim": 128}), par(right={"heads": 10, "dim": 256})]),
     "window_of_one": bare([par(mask={"size": 1, "pool": 3}), par(mask={"size": 2, "pool": 1})]),
     "window_of_a_page": bare([par(mask={"size": 64, "pool": 8}), par(mask={"size": 65, "pool": 7}), par(mask={"size": 63, "pool": 64})]),
     "window_wider_than_the_prompt": bare([par(mask={"size": 4000, "pool": 4})]),
