@@ -1,5 +1,5 @@
 #!/bin/bash
-# Multi-GPU legs of round 2 (every command under its own timeout):  bash tools/gpu_multi_r02.sh <N>
+# Multi-GPU legs (every command under its own timeout):  bash tools/gpu_multi_r02.sh <N>
 #   N=2: config 4 (70B-dims layer swap) + decode at the driver's settings      N=4: long-prompt pipeline, MoE, decode
 #   N=8: decode at the driver's settings + MoE (config 5 shape: 8 shards, 8 requests in flight)
 N=${1:-2}
